@@ -1,0 +1,172 @@
+/*
+ * kvmig — C ABI of the paged-KV block migration / swap library for B200.
+ *
+ * Every entry point takes plain pointers, integers and an opaque stream, and
+ * returns 0 on success or a negative KVMIG_E* code; the text of the last
+ * failure on the calling thread is available from kvmig_last_error().  Nothing
+ * is launched when validation fails.  There is no CPU fallback: without a CUDA
+ * device every compute entry point returns KVMIG_ECUDA.
+ *
+ * The functions replace the four native operators that DistServe resolves from
+ * SwiftTransformer's libst_pybinding.so (distserve/__init__.py:4-16).  The
+ * operator shim in libst_pybinding.so (same directory as this library) binds
+ * them under the operator names the reference calls.
+ *
+ * Pool layout, both stages, K and V separately (distserve/worker.py:107-121):
+ *   [num_blocks, layers_local, kv_heads_local, block_size, head_dim], contiguous.
+ * Parallel-config vectors use ParallelConfig.to_list() order
+ *   [tp_size, tp_rank, pp_size, pp_rank]            (distserve/config.py:57-63).
+ */
+#ifndef KVMIG_H_
+#define KVMIG_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define KVMIG_ABI_VERSION 1
+
+#if defined(__GNUC__)
+#define KVMIG_API __attribute__((visibility("default")))
+#else
+#define KVMIG_API
+#endif
+
+/* Number of int64 words in an exported pool handle (a plain int list, so it
+ * survives pickling between worker processes; distserve/utils.py:73). */
+#define KVMIG_HANDLE_WORDS 24
+
+enum {
+    KVMIG_OK = 0,
+    KVMIG_EINVAL = -1,     /* bad argument: shape, length, id out of range, duplicate target, bad handle words */
+    KVMIG_ENOTREG = -2,    /* a context worker needed for this copy was never registered */
+    KVMIG_ECUDA = -3,      /* a CUDA runtime call failed (text in kvmig_last_error) */
+    KVMIG_EDEVICE = -4,    /* the copy kernel reported a device-side problem (bounded wait ran out) */
+    KVMIG_ELIMIT = -5      /* a fixed capacity was exceeded */
+};
+
+/* Shape of one pool as the worker allocated it (distserve/worker.py:109-121). */
+typedef struct kvmig_pool_shape {
+    int64_t num_blocks;
+    int64_t num_layers;   /* layers held by this worker   = L / pp_size */
+    int64_t num_heads;    /* KV heads held by this worker = H / tp_size */
+    int64_t block_size;   /* token slots per block */
+    int64_t head_dim;
+    int64_t elem_size;    /* bytes per value: 2 for fp16/bf16, 4 for fp32 */
+} kvmig_pool_shape;
+
+KVMIG_API int kvmig_abi_version(void);
+
+/* Text of the most recent failure on this thread ("" if none). */
+KVMIG_API const char* kvmig_last_error(void);
+
+/*
+ * Export a pool so that another worker process on the same node can map it.
+ * Replaces torch.ops.block_migration_ops.get_ipc_mem_handle(Tensor) -> int[]
+ * (distserve/worker.py:133-134).  `pool` is the device address of element 0;
+ * `handle_out` receives KVMIG_HANDLE_WORDS words: the CUDA IPC handle of the
+ * enclosing allocation, the pool's byte offset inside it, its shape, and the
+ * exporter's pid (a handle registered by the process that exported it is
+ * resolved without CUDA IPC, which cannot open its own handles).
+ */
+KVMIG_API int kvmig_get_ipc_mem_handle(const void* pool, const kvmig_pool_shape* shape, int64_t* handle_out);
+
+/*
+ * Make one context-stage worker's K and V pools addressable from the calling
+ * (decoding-stage) worker.  Replaces
+ * torch.ops.block_migration_ops.register_ipc_mem_handle(k_handle, v_handle,
+ *   num_layers, num_heads, context_parallel_config, decoding_parallel_config)
+ * (distserve/worker.py:239-246).  num_layers / num_heads are the model's
+ * global counts; ctx_parallel_config names the exporting worker and
+ * dec_parallel_config the caller, both in to_list() order.  Handles of
+ * context workers whose layer/head rectangle does not meet the caller's are
+ * recorded but not mapped.  Registering the same context rank again replaces
+ * the earlier entry.  Mappings live until the process exits: the reference has
+ * no unregister call site.
+ */
+KVMIG_API int kvmig_register_ipc_mem_handle(const int64_t* k_handle, int64_t k_handle_len,
+                                  const int64_t* v_handle, int64_t v_handle_len,
+                                  int64_t num_layers, int64_t num_heads,
+                                  const int64_t* ctx_parallel_config,
+                                  const int64_t* dec_parallel_config);
+
+/*
+ * Pull blocks from the registered context workers into this worker's pools:
+ * for X in {K,V}, every i, every global layer l and KV head h this worker
+ * holds,
+ *   X_dec[dec_blocks[i], l - l0_dec, h - h0_dec, :, :] =
+ *   X_ctx(owner of l,h)[ctx_blocks[i], l - l0_ctx, h - h0_ctx, :, :].
+ * Replaces torch.ops.block_migration_ops.migrate_blocks(ctx_pp, ctx_tp,
+ *   ctx_blocks, dec_pp, dec_tp, dec_pp_rank, dec_tp_rank, dec_blocks,
+ *   k_cache, v_cache)                              (distserve/worker.py:256-267;
+ * note the pp-then-tp argument order).  The copy kernel is launched on
+ * `stream` (a cudaStream_t, NULL = the legacy default stream) and the call
+ * returns only after the kernel has finished, because the caller frees the
+ * source blocks as soon as it returns
+ * (distserve/single_stage_engine.py:524-536).
+ */
+KVMIG_API int kvmig_migrate_blocks(int64_t ctx_pp_size, int64_t ctx_tp_size,
+                         const int64_t* ctx_blocks, int64_t num_ctx_blocks,
+                         int64_t dec_pp_size, int64_t dec_tp_size,
+                         int64_t dec_pp_rank, int64_t dec_tp_rank,
+                         const int64_t* dec_blocks, int64_t num_dec_blocks,
+                         void* k_cache, void* v_cache, const kvmig_pool_shape* shape,
+                         void* stream);
+
+/*
+ * Same copy, not awaited: the kernel is enqueued on `stream` and `*ticket`
+ * identifies it.  kvmig_migrate_wait(ticket) blocks until that kernel has
+ * finished and returns its status; source blocks must not be reused before.
+ * Lets a caller enqueue a request's migration beside an in-flight decode step
+ * (the call cadence of distserve/decoding_stage_scheduler.py:247-260 is one
+ * awaited request at a time).  At most KVMIG_MAX_INFLIGHT tickets may be
+ * outstanding per device; older ones are awaited implicitly.
+ */
+#define KVMIG_MAX_INFLIGHT 8
+KVMIG_API int kvmig_migrate_blocks_async(int64_t ctx_pp_size, int64_t ctx_tp_size,
+                               const int64_t* ctx_blocks, int64_t num_ctx_blocks,
+                               int64_t dec_pp_size, int64_t dec_tp_size,
+                               int64_t dec_pp_rank, int64_t dec_tp_rank,
+                               const int64_t* dec_blocks, int64_t num_dec_blocks,
+                               void* k_cache, void* v_cache, const kvmig_pool_shape* shape,
+                               void* stream, uint64_t* ticket);
+KVMIG_API int kvmig_migrate_wait(uint64_t ticket);
+
+/*
+ * Copy whole blocks between the GPU pools and the pinned host pools, in list
+ * order, on `stream`, without waiting for completion.  Replaces
+ * torch.ops.swapping_ops.swap(source_block_ids, target_block_ids, is_swap_in,
+ *   k_cache, v_cache, k_swap, v_swap)              (distserve/worker.py:303-311).
+ * is_swap_in != 0: host block source[i] -> GPU block target[i]; else GPU block
+ * source[i] -> host block target[i].  `shape` describes the GPU pools; the
+ * host pools have the same per-block shape and num_cpu_blocks blocks
+ * (distserve/worker.py:122-130).
+ */
+KVMIG_API int kvmig_swap(const int64_t* source_block_ids, int64_t num_source,
+               const int64_t* target_block_ids, int64_t num_target,
+               int is_swap_in,
+               void* k_cache, void* v_cache, const kvmig_pool_shape* shape,
+               void* k_swap, void* v_swap, int64_t num_cpu_blocks,
+               void* stream);
+
+/*
+ * Tuning and introspection (no counterpart in the reference).
+ *   options : "kernel" 0 auto | 1 vector loads | 2 bulk-copy pipeline,
+ *             "chunk_bytes", "stages", "ctas_per_sm", "swap_kernel" (0/1)
+ *   counters: "kernel_launches", "memcpy_calls", "bytes_migrated",
+ *             "bytes_swapped", "mapped_peers"
+ */
+KVMIG_API int kvmig_set_option(const char* name, int64_t value);
+KVMIG_API int64_t kvmig_get_option(const char* name);
+KVMIG_API int64_t kvmig_get_counter(const char* name);
+
+/* Forget every registered context worker of the current device (test use;
+ * mapped peer allocations stay mapped and are reused on re-registration). */
+KVMIG_API int kvmig_reset_registry(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* KVMIG_H_ */

@@ -1,0 +1,293 @@
+"""Regenerates the fixtures in this directory from the UNMODIFIED reference
+Python package.  Run once, where the reference checkout is available:
+
+    python tests/golden/make_golden.py /path/to/reference
+
+The reference's native library is absent, so nothing here executes the copy
+itself; what the fixtures pin is everything the reference's own code decides
+on this path:
+
+* geometry.json       — ModelConfig.get_num_layers / get_num_heads /
+                        get_head_size and ParallelConfig.to_list() for the
+                        benchmark model shapes and stage layouts;
+* block_manager.json  — every block table and every worker call produced by
+                        the reference BlockManager over a seeded sequence of
+                        allocate / extend / free / swap-out / swap-in steps;
+* worker_calls.json   — the exact positional arguments the reference
+                        ParaWorker passes to the four native operators.
+
+``ray`` is not installed; a stub whose ``remote`` returns the class unchanged
+is injected so that the reference modules import.
+"""
+from __future__ import annotations
+
+import json
+import os
+import random
+import sys
+import tempfile
+import types
+from pathlib import Path
+
+HERE = Path(__file__).resolve().parent
+ROOT = HERE.parent.parent
+
+MODEL_SHAPES = {
+    # name: HuggingFace config fields that the geometry methods read
+    "opt-125m": dict(model_type="opt", hidden_size=768, num_attention_heads=12, num_hidden_layers=12,
+                     max_position_embeddings=2048, vocab_size=50272, ffn_dim=3072),
+    "opt-13b": dict(model_type="opt", hidden_size=5120, num_attention_heads=40, num_hidden_layers=40,
+                    max_position_embeddings=2048, vocab_size=50272, ffn_dim=20480),
+    "llama-2-13b": dict(model_type="llama", hidden_size=5120, num_attention_heads=40, num_key_value_heads=40,
+                        num_hidden_layers=40, max_position_embeddings=4096, vocab_size=32000, intermediate_size=13824),
+    "llama-2-70b": dict(model_type="llama", hidden_size=8192, num_attention_heads=64, num_key_value_heads=8,
+                        num_hidden_layers=80, max_position_embeddings=4096, vocab_size=32000, intermediate_size=28672),
+    "llama-2-7b": dict(model_type="llama", hidden_size=4096, num_attention_heads=32, num_key_value_heads=32,
+                       num_hidden_layers=32, max_position_embeddings=4096, vocab_size=32000, intermediate_size=11008),
+}
+LAYOUTS = [(1, 1), (2, 1), (1, 2), (2, 2), (4, 1), (4, 2), (8, 1)]   # (tp, pp)
+
+
+def import_reference(ref_root: str):
+    ray = types.ModuleType("ray")
+    ray.remote = lambda *a, **k: (a[0] if a and callable(a[0]) and not k else (lambda cls: cls))
+    ray.get_gpu_ids = lambda: [0]
+    for name in ("ray.util", "ray.util.placement_group", "ray.util.scheduling_strategies"):
+        sys.modules[name] = types.ModuleType(name)
+    sys.modules["ray.util.placement_group"].PlacementGroup = object
+    sys.modules["ray.util.scheduling_strategies"].PlacementGroupSchedulingStrategy = object
+    ray.util = sys.modules["ray.util"]
+    sys.modules["ray"] = ray
+    # distserve/__init__.py insists on loading a shared library; any loadable one will do.
+    sys.path.insert(0, str(ROOT))
+    from distserve_b200 import kvmig_library_path
+
+    os.environ["SWIFT_TRANSFORMER_LIB_PATH"] = str(kvmig_library_path())
+    sys.path.insert(0, ref_root)
+    import distserve  # noqa: F401
+    return distserve
+
+
+def write_hf_dir(tmp: str, name: str) -> str:
+    d = os.path.join(tmp, name)
+    os.makedirs(d, exist_ok=True)
+    with open(os.path.join(d, "config.json"), "w") as f:
+        json.dump(MODEL_SHAPES[name], f)
+    return d
+
+
+def golden_geometry(tmp: str):
+    from distserve.config import ModelConfig, ParallelConfig
+
+    out = []
+    for name in MODEL_SHAPES:
+        mc = ModelConfig(write_hf_dir(tmp, name), None)
+        for tp, pp in LAYOUTS:
+            try:
+                pc = ParallelConfig(tp, tp - 1, pp, pp - 1)
+                out.append(dict(model=name, tp=tp, pp=pp, layers_total=mc.get_num_layers(), heads_total=mc.get_num_heads(),
+                                layers_local=mc.get_num_layers(pc), heads_local=mc.get_num_heads(pc),
+                                head_size=mc.get_head_size(), dtype_size=mc.get_dtype_size(), to_list=pc.to_list()))
+            except AssertionError:
+                out.append(dict(model=name, tp=tp, pp=pp, error="not divisible"))
+    return out
+
+
+def state_digest(bm) -> str:
+    """Digest of every block table, location and free/parked list of a block manager."""
+    import hashlib
+
+    state = [sorted((k, list(v)) for k, v in bm.block_table.items()),
+             sorted((k, v.value) for k, v in bm.request_location.items()),
+             list(bm.free_gpu_blocks_list), list(bm.free_cpu_blocks_list),
+             list(bm.swapping_gpu_blocks_list), list(bm.swapping_cpu_blocks_list)]
+    return hashlib.sha1(json.dumps(state, separators=(",", ":")).encode()).hexdigest()[:16]
+
+
+def golden_block_manager(tmp: str):
+    from distserve.block_manager import BlockManager
+    from distserve.config import CacheConfig, ModelConfig, ParallelConfig
+    from distserve.request import Request
+    from distserve.utils import Stage
+
+    mc = ModelConfig(write_hf_dir(tmp, "opt-125m"), None)
+    calls = []
+
+    def record(name, *args):
+        if name == "swap_blocks":
+            reqs, src, dst, is_in = args
+            calls.append([name, [r.request_id for r in reqs], list(src), list(dst), bool(is_in)])
+        else:
+            calls.append([name])
+
+    scenarios = []
+    for seed, (gpu_blocks, cpu_blocks, block_size) in enumerate([(64, 48, 16), (40, 40, 8), (128, 64, 16)]):
+        rng = random.Random(7000 + seed)
+        bm = BlockManager(Stage.DECODING, gpu_blocks, cpu_blocks, mc, ParallelConfig(), CacheConfig(block_size, 256), record)
+        live, on_cpu, steps, next_id = {}, set(), [], 0
+        for _ in range(300):
+            calls.clear()
+            choices = ["alloc"]
+            if live:
+                choices += ["extend", "free", "swap_out", "swap_in"]
+            op = rng.choice(choices)
+            entry = {"op": op}
+            try:
+                if op == "alloc":
+                    n = rng.randint(1, 5 * block_size)
+                    req = Request(0.0, next_id, "", [0] * n)
+                    need = bm.get_num_blocks_needed(req)
+                    if need > bm.get_num_avail_gpu_blocks():
+                        continue
+                    bm.allocate_blocks(req)
+                    live[next_id] = req
+                    entry.update(request_id=next_id, prompt_len=n)
+                    next_id += 1
+                elif op == "extend":
+                    rid = rng.choice(sorted(set(live) - on_cpu) or [None])
+                    if rid is None:
+                        continue
+                    req = live[rid]
+                    k = rng.randint(1, 2 * block_size)
+                    for _ in range(k):
+                        req.generated_tokens.append("")
+                        req.generated_token_ids.append(0)
+                    if bm.get_num_append_blocks_needed(req) > bm.get_num_avail_gpu_blocks():
+                        for _ in range(k):
+                            req.generated_tokens.pop()
+                            req.generated_token_ids.pop()
+                        continue
+                    bm.allocate_blocks(req)
+                    entry.update(request_id=rid, new_tokens=k)
+                elif op == "free":
+                    rid = rng.choice(sorted(live))
+                    bm.free_blocks(rid)
+                    live.pop(rid)
+                    on_cpu.discard(rid)
+                    entry.update(request_id=rid)
+                elif op == "swap_out":
+                    cands = sorted(set(live) - on_cpu)
+                    if not cands:
+                        continue
+                    picked = rng.sample(cands, min(len(cands), rng.randint(1, 2)))
+                    if sum(len(bm.block_table[r]) for r in picked) > bm.get_num_avail_cpu_blocks():
+                        continue
+                    bm.swap_out_requests([live[r] for r in picked])
+                    on_cpu.update(picked)
+                    entry.update(request_ids=picked)
+                elif op == "swap_in":
+                    cands = sorted(on_cpu)
+                    if not cands:
+                        continue
+                    picked = rng.sample(cands, min(len(cands), rng.randint(1, 2)))
+                    if sum(len(bm.block_table[r]) for r in picked) > bm.get_num_avail_gpu_blocks():
+                        continue
+                    bm.swap_in_requests([live[r] for r in picked])
+                    on_cpu.difference_update(picked)
+                    entry.update(request_ids=picked)
+            except AssertionError as e:   # recorded: the mirror must refuse the same step
+                entry["assertion"] = str(e)[:40]
+            entry["calls"] = [list(c) for c in calls]
+            touched = entry.get("request_ids", [entry["request_id"]] if "request_id" in entry else [])
+            entry["touched"] = {str(r): list(bm.block_table[r]) for r in touched if r in bm.block_table}
+            entry["digest"] = state_digest(bm)
+            entry["avail"] = [bm.get_num_avail_gpu_blocks(), bm.get_num_avail_cpu_blocks()]
+            steps.append(entry)
+        scenarios.append(dict(gpu_blocks=gpu_blocks, cpu_blocks=cpu_blocks, block_size=block_size, steps=steps))
+    return scenarios
+
+
+def golden_worker_calls(tmp: str):
+    """Drive the reference ParaWorker's KV methods with recording stand-ins for
+    the native operators and a meta-device torch.empty, and keep the arguments."""
+    import torch
+    from distserve.config import CacheConfig, ModelConfig, ParallelConfig
+    from distserve.utils import Stage
+    from distserve.worker import ParaWorker
+
+    recorded = []
+
+    class Recorder:
+        def __init__(self, ns):
+            self.ns = ns
+
+        def __getattr__(self, op):
+            def call(*args):
+                norm = []
+                for a in args:
+                    if isinstance(a, torch.Tensor):
+                        norm.append({"tensor": list(a.shape), "dtype": str(a.dtype)})
+                    else:
+                        norm.append(a)
+                recorded.append({"op": f"{self.ns}.{op}", "args": norm})
+                return [len(recorded)] * 3 if op == "get_ipc_mem_handle" else None
+            return call
+
+    torch.ops.block_migration_ops = Recorder("block_migration_ops")
+    torch.ops.swapping_ops = Recorder("swapping_ops")
+    real_empty, real_sync = torch.empty, torch.cuda.synchronize
+    torch.empty = lambda shape, dtype=None, device=None, pin_memory=False: real_empty(shape, dtype=dtype, device="meta")
+    torch.cuda.synchronize = lambda *a, **k: None
+
+    class FakeStream:
+        def __enter__(self):
+            return self
+
+        def __exit__(self, *a):
+            return False
+
+    real_stream_ctx, real_event = torch.cuda.stream, torch.cuda.Event
+    torch.cuda.stream = lambda s: FakeStream()
+
+    class FakeEvent:
+        def record(self, stream=None):
+            pass
+
+        def wait(self, stream=None):
+            pass
+
+    torch.cuda.Event = FakeEvent
+    cases = []
+    try:
+        for model, (ctx_tp, ctx_pp), (dec_tp, dec_pp) in [("opt-125m", (1, 1), (1, 1)), ("llama-2-13b", (2, 1), (1, 1)),
+                                                          ("llama-2-70b", (4, 1), (2, 2))]:
+            mc = ModelConfig(write_hf_dir(tmp, model), None)
+            for dp in range(dec_pp):
+                for dt in range(dec_tp):
+                    recorded.clear()
+                    w = object.__new__(ParaWorker)
+                    w.model_config, w.cache_config = mc, CacheConfig(16, 256)
+                    w.parallel_config = ParallelConfig(dec_tp, dt, dec_pp, dp)
+                    w.stage = Stage.DECODING
+                    w.swap_in_stream = w.swap_out_stream = object()
+                    w.swap_event_table = {}
+                    w.latest_swap_in_event = w.latest_swap_out_event = None
+                    handles_back = w.init_kvcache_and_swap(32, 8)
+                    table = [[([1000 + p * 10 + t], [2000 + p * 10 + t]) for t in range(ctx_tp)] for p in range(ctx_pp)]
+                    ctx_pc = ParallelConfig(ctx_tp, 0, ctx_pp, 0)
+                    w.register_kvcache_mem_handles(ctx_pc, table)
+                    w.migrate_blocks([3, 1, 4], ctx_pc, [9, 2, 6])
+                    w.swap_blocks([11], [5, 6], [0, 1], False)
+                    w.swap_blocks([11], [0, 1], [7, 8], True)
+                    cases.append(dict(model=model, ctx=[ctx_tp, ctx_pp], dec=[dec_tp, dt, dec_pp, dp],
+                                      init_returned=[list(h) for h in handles_back], calls=[dict(c) for c in recorded]))
+    finally:
+        torch.empty, torch.cuda.synchronize = real_empty, real_sync
+        torch.cuda.stream, torch.cuda.Event = real_stream_ctx, real_event
+    return cases
+
+
+def main():
+    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    import_reference(ref_root)
+    with tempfile.TemporaryDirectory() as tmp:
+        for name, fn in (("geometry", golden_geometry), ("block_manager", golden_block_manager),
+                         ("worker_calls", golden_worker_calls)):
+            data = fn(tmp)
+            with open(HERE / f"{name}.json", "w") as f:
+                json.dump(data, f, separators=(",", ":"))
+            print(name, len(data), "entries,", (HERE / f"{name}.json").stat().st_size, "bytes")
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,154 @@
+"""The full call chain of the reference — stage engines, block managers,
+workers, operator shim — on the OPT-125M-shaped workload and on resharded
+layouts, replayed against the oracle; plus two worker processes exchanging
+CUDA IPC handles."""
+import multiprocessing as mp
+
+import numpy as np
+import pytest
+import torch
+
+from distserve_b200 import capi
+from distserve_b200.config import CacheConfig, KVModelConfig, ParallelConfig
+from distserve_b200.request import Request
+from distserve_b200.stage import ContextStageEngine, DecodingStageEngine
+from distserve_b200.worker import KVWorker
+from distserve_b200.workloads import WORKLOADS, make_trace, prompt_lengths
+from oracle import kv_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+
+def build_stages(model, block_size, ctx, dec, ctx_blocks, dec_blocks, seed):
+    cache = CacheConfig(block_size, 1 << 20)
+
+    def grid(stage, pc):
+        return [[KVWorker(p * pc.tensor_parallel_size + t, stage, model, cache, pc.with_rank(p, t))
+                 for t in range(pc.tensor_parallel_size)] for p in range(pc.pipeline_parallel_size)]
+
+    ctx_engine = ContextStageEngine(model, ctx, cache, grid("context", ctx))
+    dec_engine = DecodingStageEngine(model, dec, cache, grid("decoding", dec),
+                                     clear_migrated_blocks_callback=ctx_engine.clear_migrated_blocks)
+    handles = ctx_engine.init_kvcache(ctx_blocks, 1)
+    dec_engine.init_kvcache(dec_blocks, 1)
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    for engine in (ctx_engine, dec_engine):
+        for row in engine.workers:
+            for w in row:
+                for pool in (w.k_cache, w.v_cache):
+                    pool.copy_(torch.randn(pool.shape, device="cuda", generator=g).to(pool.dtype))
+    dec_engine.register_kvcache_mem_handles(ctx, handles)
+    return ctx_engine, dec_engine
+
+
+def host_copy(engine):
+    return {(p, t): (w.k_cache.cpu().view(torch.int16).numpy().copy(), w.v_cache.cpu().view(torch.int16).numpy().copy())
+            for p, row in enumerate(engine.workers) for t, w in enumerate(row)}
+
+
+def run_and_check(model, block_size, ctx, dec, ctx_blocks, dec_blocks, lengths, seed):
+    capi.reset_registry()
+    ctx_engine, dec_engine = build_stages(model, block_size, ctx, dec, ctx_blocks, dec_blocks, seed)
+    src_host, dst_host = host_copy(ctx_engine), host_copy(dec_engine)
+    resident = []
+    for rid, n in enumerate(lengths):
+        req = Request.of_length(rid, n)
+        need = -(-n // block_size)
+        while dec_engine.block_manager.get_num_avail_gpu_blocks() < need:
+            dec_engine.block_manager.free_blocks(resident.pop(0))
+        migrating = ctx_engine.finish_prefill(req)
+        req.append_token()                                   # the prefill step produced one token
+        target = dec_engine.migrate_blocks(migrating)
+        resident.append(rid)
+        assert len(target) == need == len(migrating.block_indexes)
+        assert dec_engine.migration_latency(rid) > 0
+        for (p, t), (k, v) in dst_host.items():
+            O.migrate_blocks_numpy(src_host, ctx.tensor_parallel_size, ctx.pipeline_parallel_size, migrating.block_indexes,
+                                   dec.tensor_parallel_size, t, dec.pipeline_parallel_size, p, target, k, v,
+                                   model.num_layers, model.num_kv_heads)
+    assert ctx_engine.block_manager.get_num_avail_gpu_blocks() == ctx_blocks      # every source block was recycled
+    got = host_copy(dec_engine)
+    for key in dst_host:
+        assert np.array_equal(got[key][0], dst_host[key][0]) and np.array_equal(got[key][1], dst_host[key][1]), key
+
+
+def test_opt125m_workload_end_to_end():
+    """32 requests, lengths U[64,512], 512-block pools on both sides: total
+    demand exceeds a pool, so ids are recycled as the engines recycle them."""
+    w = WORKLOADS["c1"]
+    lengths = prompt_lengths(w)
+    assert len(lengths) == 32 and sum(-(-n // 16) for n in lengths) > 512
+    run_and_check(w.model, w.block_size, w.ctx_config(), w.dec_config(), 512, 512, lengths, seed=21)
+
+
+@pytest.mark.parametrize("name,model", [("c3", KVModelConfig(4, 8, 32)), ("c4", KVModelConfig(8, 8, 32)),
+                                        ("c5", KVModelConfig(4, 8, 32))])
+def test_resharded_layouts_end_to_end(name, model):
+    """The benchmark's tensor/pipeline reshard layouts with a scaled-down model."""
+    w = WORKLOADS[name]
+    rng = np.random.default_rng(22)
+    lengths = [int(x) for x in rng.integers(1, 200, size=24)]
+    run_and_check(model, 16, w.ctx_config(), w.dec_config(), 48, 40, lengths, seed=23)
+
+
+def test_trace_replay_matches_engine_flow():
+    """make_trace() (used by the benchmark) yields the ids the engines yield."""
+    w = WORKLOADS["c1"]
+    trace = make_trace(w)
+    assert [t.prompt_len for t in trace] == prompt_lengths(w)
+    for item in trace:
+        assert len(item.src_blocks) == len(item.dst_blocks) == -(-item.prompt_len // w.block_size)
+        assert len(set(item.dst_blocks)) == len(item.dst_blocks)
+
+
+def _context_process(conn, device, seed):
+    """A context-stage worker in its own process: fills its pools from the
+    seed, sends the handles, stays alive until told to stop."""
+    torch.cuda.set_device(device)
+    model, cache = KVModelConfig(4, 4, 32), CacheConfig(8, 64)
+    worker = KVWorker(0, "context", model, cache, ParallelConfig(), device=device)
+    handles = worker.init_kvcache_and_swap(20, 1)
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    worker.k_cache.copy_(torch.randn(worker.k_cache.shape, generator=g).half())
+    worker.v_cache.copy_(torch.randn(worker.v_cache.shape, generator=g).half())
+    torch.cuda.synchronize()
+    conn.send(handles)
+    conn.recv()
+
+
+def test_two_processes_share_pools_through_ipc_handles():
+    """The decoding worker opens a handle exported by ANOTHER process (on the
+    second GPU when there is one, else on the same GPU)."""
+    ctxmp = mp.get_context("spawn")
+    parent, child = ctxmp.Pipe()
+    src_device = 1 if torch.cuda.device_count() > 1 else 0
+    proc = ctxmp.Process(target=_context_process, args=(child, src_device, 31), daemon=True)
+    proc.start()
+    try:
+        assert parent.poll(180), "context process did not report its handles"
+        k_handle, v_handle = parent.recv()
+        assert len(k_handle) == capi.HANDLE_WORDS and k_handle[11] == proc.pid
+        capi.reset_registry()
+        model, cache = KVModelConfig(4, 4, 32), CacheConfig(8, 64)
+        mapped_before = capi.get_counter("mapped_peers")
+        for t in range(2):                                  # decoding stage tp=2 pulling from a tp=1 context worker
+            dec = KVWorker(t, "decoding", model, cache, ParallelConfig(2, t, 1, 0), device=0)
+            dec.init_kvcache_and_swap(16, 1)
+            dec.k_cache.zero_()
+            dec.v_cache.zero_()
+            dec.register_kvcache_mem_handles(ParallelConfig(), [[(k_handle, v_handle)]])
+            src, dst = [19, 0, 7], [2, 15, 3]
+            dec.migrate_blocks(src, ParallelConfig(), dst)
+            g = torch.Generator(device="cpu").manual_seed(31)
+            ref_k = torch.randn(20, 4, 4, 8, 32, generator=g).half()
+            ref_v = torch.randn(20, 4, 4, 8, 32, generator=g).half()
+            assert torch.equal(dec.k_cache[dst].cpu(), ref_k[src][:, :, 2 * t:2 * t + 2])
+            assert torch.equal(dec.v_cache[dst].cpu(), ref_v[src][:, :, 2 * t:2 * t + 2])
+            untouched = [i for i in range(16) if i not in dst]
+            assert not dec.k_cache[untouched].any() and not dec.v_cache[untouched].any()
+        assert capi.get_counter("mapped_peers") - mapped_before >= 1      # really went through cudaIpcOpenMemHandle
+    finally:
+        parent.send("stop")
+        proc.join(30)
+        if proc.is_alive():
+            proc.kill()
