@@ -273,8 +273,11 @@ int64_t handle_checksum(const int64_t* w) {
     return (int64_t)h;
 }
 
+// Defaults from a sweep on B200 (OPT-13B-shaped blocks, same-GPU copy): 8 KiB chunks, a
+// 3-stage ring and 3 CTAs per SM keep about 72 KiB in flight per SM, where HBM throughput
+// peaks; more bytes in flight lowered it again.
 struct Options {
-    std::atomic<int64_t> kernel{0}, chunk_bytes{16384}, stages{4}, ctas_per_sm{0};
+    std::atomic<int64_t> kernel{0}, chunk_bytes{8192}, stages{3}, ctas_per_sm{0};
 };
 Options g_opt;
 
@@ -609,7 +612,11 @@ int enqueue_migration(int64_t ctx_pp, int64_t ctx_tp, const int64_t* ctx_blocks,
         if ((int64_t)smem > st.max_smem_optin)
             return fail(KVMIG_ELIMIT, "stages x chunk_bytes = %zu B exceeds the %d B of shared memory a CTA may use", smem,
                         st.max_smem_optin);
-        if (ctas_per_sm <= 0) ctas_per_sm = std::max<int64_t>(1, std::min<int64_t>(8, (220 * 1024) / (int64_t)(smem + 1024)));
+        if (ctas_per_sm <= 0) {
+            const int64_t ring = stages * chunk, target = 72 * 1024;   // bytes in flight per SM
+            ctas_per_sm = std::max<int64_t>(1, std::min<int64_t>(8, (target + ring - 1) / ring));
+            ctas_per_sm = std::min<int64_t>(ctas_per_sm, std::max<int64_t>(1, (220 * 1024) / (int64_t)(smem + 1024)));
+        }
         if ((int)smem > st.bulk_smem_set) {
             CU_TRY(cudaFuncSetAttribute(kv_migrate_bulk, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
             st.bulk_smem_set = (int)smem;

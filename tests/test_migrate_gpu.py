@@ -80,13 +80,15 @@ def test_odd_shapes_fall_back_to_narrower_vectors(B, D, elem):
     automatic selection must still be bit-exact."""
     rng = np.random.default_rng(B * 100 + D)
     cs = Stage(4, 4, 2, 2, 11, B, D, elem_size=elem, seed=5)
-    ds = Stage(4, 4, 1, 1, 13, B, D, elem_size=elem, seed=6)
-    register_all(cs, ds)
     src, dst = ragged_lists(rng, 11, 13, 9)
-    migrate_all(cs, ds, src, dst)
-    oracle_all(cs, ds, src, dst)
-    assert_stage_equals_host(ds)
-    if (B * D * elem) % 16:
+    for dec_tp, dec_pp in ((1, 1), (4, 1)):               # whole blocks, then single-head runs
+        capi.reset_registry()
+        ds = Stage(4, 4, dec_tp, dec_pp, 13, B, D, elem_size=elem, seed=6)
+        register_all(cs, ds)
+        migrate_all(cs, ds, src, dst)
+        oracle_all(cs, ds, src, dst)
+        assert_stage_equals_host(ds)
+    if (B * D * elem) % 16:                               # ds now copies one head (= one slab) per run
         capi.set_option("kernel", 2)
         with pytest.raises(capi.KvmigError, match="16-byte"):
             migrate_all(cs, ds, src, dst)
