@@ -49,6 +49,8 @@ SIGNATURES = {
                                              C.c_int64, _I64P, C.c_int64, C.c_void_p, C.c_void_p, _SHAPEP, C.c_void_p,
                                              C.POINTER(C.c_uint64)]),
     "kvmig_migrate_wait": (C.c_int, [C.c_uint64]),
+    "kvmig_migrate_blocks_static": (C.c_int, [C.c_int64, C.c_int64, _I64P, C.c_int64, C.c_int64, C.c_int64, C.c_int64,
+                                              C.c_int64, _I64P, C.c_int64, C.c_void_p, C.c_void_p, _SHAPEP, C.c_void_p]),
     "kvmig_swap": (C.c_int, [_I64P, C.c_int64, _I64P, C.c_int64, C.c_int, C.c_void_p, C.c_void_p, _SHAPEP, C.c_void_p,
                              C.c_void_p, C.c_int64, C.c_void_p]),
     "kvmig_set_option": (C.c_int, [C.c_char_p, C.c_int64]),
@@ -107,6 +109,18 @@ def migrate_blocks_async(ctx_pp, ctx_tp, ctx_blocks, dec_pp, dec_tp, dec_pp_rank
                                             dec_pp_rank, dec_tp_rank, _i64(dec_blocks), len(dec_blocks), k_ptr, v_ptr,
                                             C.byref(shape), stream, C.byref(ticket)))
     return ticket.value
+
+
+STATIC_MAX_BLOCKS = 4096
+
+
+def migrate_blocks_static(ctx_pp, ctx_tp, ctx_blocks, dec_pp, dec_tp, dec_pp_rank, dec_tp_rank, dec_blocks,
+                          k_ptr: int, v_ptr: int, shape: PoolShape, stream: int = 0) -> None:
+    """kvmig_migrate_blocks_static: the same copy for hosts that may not allocate device memory
+    once serving has started; at most STATIC_MAX_BLOCKS blocks per call."""
+    _check(lib().kvmig_migrate_blocks_static(ctx_pp, ctx_tp, _i64(ctx_blocks), len(ctx_blocks), dec_pp, dec_tp,
+                                             dec_pp_rank, dec_tp_rank, _i64(dec_blocks), len(dec_blocks), k_ptr, v_ptr,
+                                             C.byref(shape), stream))
 
 
 def migrate_wait(ticket: int) -> None:

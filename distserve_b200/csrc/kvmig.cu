@@ -716,6 +716,205 @@ int wait_ticket(uint64_t ticket) {
     return rc;
 }
 
+
+// ---------------------------------------------------------------------------
+// Allocation-free variant of the migration entry point
+// ---------------------------------------------------------------------------
+//
+// kvmig_migrate_blocks needs a little device scratch besides the pools: the two
+// int32 block tables and a status word.  It gets them from cudaMalloc /
+// cudaHostAlloc on first use.  Some hosts must not allocate once serving has
+// started: a decoding worker sizes its KV pools from whatever HBM is free
+// (distserve/worker.py:152-192), so a later cudaMalloc may fail or stall the
+// device in the middle of a decode loop, and some embedders forbid allocation
+// after start-up altogether.  For them the scratch below is part of the loaded
+// module: every GPU that loads this library holds these 33 KiB until exit.
+//
+// In host code `g_static_scratch` is only a stand-in symbol, not a device
+// address; the address is looked up once per device with cudaGetSymbolAddress
+// (with that device current) and that pointer is what the kernels receive.
+constexpr int kStaticStatusWords = 64;                        // 256 B, keeps the tables 256-byte aligned
+static __device__ __align__(256) int g_static_scratch[kStaticStatusWords + 2 * KVMIG_STATIC_MAX_BLOCKS];
+
+constexpr int kStaticMaxDevices = 64;
+int* g_static_ptr[kStaticMaxDevices];                         // device address of the array, per device ordinal
+int g_static_stage[kStaticStatusWords + 2 * KVMIG_STATIC_MAX_BLOCKS];   // host staging image, guarded by g_mu
+
+int static_scratch_for_current_device(int dev, int** out) {
+    if (dev < 0 || dev >= kStaticMaxDevices) return fail(KVMIG_ELIMIT, "device ordinal %d is beyond %d", dev, kStaticMaxDevices);
+    if (!g_static_ptr[dev]) {
+        int* ptr = nullptr;
+        cudaError_t e = cudaGetSymbolAddress((void**)&ptr, g_static_scratch);
+        if (e != cudaSuccess || !ptr)
+            return fail(KVMIG_ECUDA, "cudaGetSymbolAddress(static scratch) on device %d: %s", dev, cudaGetErrorString(e));
+        g_static_ptr[dev] = ptr;
+    }
+    *out = g_static_ptr[dev];
+    return 0;
+}
+
+int migrate_static(int64_t ctx_pp, int64_t ctx_tp, const int64_t* ctx_blocks, int64_t n_ctx, int64_t dec_pp, int64_t dec_tp,
+                   int64_t dec_pp_rank, int64_t dec_tp_rank, const int64_t* dec_blocks, int64_t n_dec, void* k_cache,
+                   void* v_cache, const kvmig_pool_shape* shape, cudaStream_t stream) {
+    g_err.clear();
+    int rc = check_shape(shape, "migrate_blocks_static");
+    if (rc) return rc;
+    if (n_ctx < 0 || n_dec < 0) return fail(KVMIG_EINVAL, "negative list length");
+    if (n_ctx != n_dec)
+        return fail(KVMIG_EINVAL, "context_block_indexes has %lld entries but decoding_block_indexes has %lld",
+                    (long long)n_ctx, (long long)n_dec);
+    if (n_ctx > KVMIG_STATIC_MAX_BLOCKS)
+        return fail(KVMIG_ELIMIT,
+                    "%lld blocks in one call exceed the %d the built-in scratch holds; split the lists or use "
+                    "kvmig_migrate_blocks",
+                    (long long)n_ctx, KVMIG_STATIC_MAX_BLOCKS);
+    if (n_ctx > 0 && (!ctx_blocks || !dec_blocks)) return fail(KVMIG_EINVAL, "block index list is NULL");
+    if (!k_cache || !v_cache) return fail(KVMIG_EINVAL, "k_cache / v_cache is NULL");
+
+    std::lock_guard<std::mutex> lock(g_mu);
+    DeviceState* stp;
+    int dev;
+    rc = ensure_device(&stp, &dev);
+    if (rc) return rc;
+    DeviceState& st = *stp;
+    int* scratch = nullptr;
+    rc = static_scratch_for_current_device(dev, &scratch);
+    if (rc) return rc;
+
+    const int64_t L = shape->num_layers * dec_pp, H = shape->num_heads * dec_tp;
+    std::vector<SegPlan> plan;
+    rc = plan_segments(L, H, ctx_tp, ctx_pp, dec_tp, dec_tp_rank, dec_pp, dec_pp_rank, &plan);
+    if (rc) return rc;
+    if (plan.size() * 2 > (size_t)kMaxSegs)
+        return fail(KVMIG_ELIMIT, "this reshard needs %zu segments; the allocation-free entry point takes %d", plan.size() * 2,
+                    kMaxSegs);
+    const int64_t slab = shape->block_size * shape->head_dim * shape->elem_size;
+    const int64_t Lc = L / ctx_pp, Hc = H / ctx_tp;
+    const int64_t chunk = g_opt.chunk_bytes.load();
+    MigParams p;
+    std::memset(&p, 0, sizeof p);
+    int64_t src_num_blocks = INT64_MAX, bytes_per_block = 0;
+    uintptr_t align_bits = 0;
+    unsigned upb = 0;
+    for (const SegPlan& sp : plan) {
+        auto it = st.registry.find(sp.ctx);
+        if (it == st.registry.end())
+            return fail(KVMIG_ENOTREG, "context worker (pp_rank %lld, tp_rank %lld) is not registered on this device",
+                        (long long)sp.ctx.pp_rank, (long long)sp.ctx.tp_rank);
+        const CtxEntry& ce = it->second;
+        if (!ce.mapped)   // mapping a peer pool reserves address space; that belongs to registration, not to this call
+            return fail(KVMIG_ENOTREG,
+                        "context worker (pp_rank %lld, tp_rank %lld) was registered for another decoding rank and is not "
+                        "mapped; register it with this worker's parallel config first",
+                        (long long)sp.ctx.pp_rank, (long long)sp.ctx.tp_rank);
+        if (ce.L != L || ce.H != H) return fail(KVMIG_EINVAL, "registered model shape differs from this worker's");
+        kvmig_pool_shape ss = shape_of_handle(ce.hk.data());
+        if (ss.block_size != shape->block_size || ss.head_dim != shape->head_dim || ss.elem_size != shape->elem_size)
+            return fail(KVMIG_EINVAL, "context pool block geometry differs from the decoding pool's");
+        src_num_blocks = std::min(src_num_blocks, std::min(ce.hk[HW_NB], ce.hv[HW_NB]));
+        for (int x = 0; x < 2; ++x) {
+            Seg g;
+            g.src_block_stride = Lc * Hc * slab;
+            g.dst_block_stride = shape->num_layers * shape->num_heads * slab;
+            g.src_row_stride = Hc * slab;
+            g.dst_row_stride = shape->num_heads * slab;
+            g.run_bytes = sp.n_heads * slab;
+            g.rows = (unsigned)sp.n_layers;
+            g.src = (x == 0 ? ce.k : ce.v) + sp.src_layer_off * g.src_row_stride + sp.src_head_off * slab;
+            g.dst = static_cast<char*>(x == 0 ? k_cache : v_cache) + sp.dst_layer_off * g.dst_row_stride + sp.dst_head_off * slab;
+            if (g.run_bytes == g.src_row_stride && g.run_bytes == g.dst_row_stride) {
+                g.run_bytes *= g.rows;
+                g.rows = 1;
+            }
+            align_bits |= (uintptr_t)g.src | (uintptr_t)g.dst | g.src_block_stride | g.dst_block_stride | g.src_row_stride |
+                          g.dst_row_stride | g.run_bytes;
+            g.chunks_per_run = (unsigned)((g.run_bytes + chunk - 1) / chunk);
+            g.units_per_block = g.rows * g.chunks_per_run;
+            g.unit_begin = upb;
+            upb += g.units_per_block;
+            bytes_per_block += (int64_t)g.run_bytes * g.rows;
+            p.seg[p.nseg++] = g;
+        }
+    }
+    for (int64_t i = 0; i < n_ctx; ++i) {
+        if (ctx_blocks[i] < 0 || ctx_blocks[i] >= src_num_blocks)
+            return fail(KVMIG_EINVAL, "context_block_indexes[%lld] = %lld is outside the context pool (%lld blocks)", (long long)i,
+                        (long long)ctx_blocks[i], (long long)src_num_blocks);
+        if (dec_blocks[i] < 0 || dec_blocks[i] >= shape->num_blocks)
+            return fail(KVMIG_EINVAL, "decoding_block_indexes[%lld] = %lld is outside the decoding pool (%lld blocks)",
+                        (long long)i, (long long)dec_blocks[i], (long long)shape->num_blocks);
+        for (int64_t j = 0; j < i; ++j)   // n <= 4096: a quadratic scan needs no memory
+            if (dec_blocks[j] == dec_blocks[i])
+                return fail(KVMIG_EINVAL, "decoding_block_indexes names block %lld twice", (long long)dec_blocks[i]);
+    }
+    if (n_ctx == 0) return 0;
+    if ((int64_t)upb * n_ctx > 0x7fffffff) return fail(KVMIG_ELIMIT, "too many work units for one launch; lower the block count");
+
+    const int vec = pick_vec(align_bits);
+    int64_t kernel = g_opt.kernel.load();
+    if (kernel == 0) kernel = (vec == 16) ? 2 : 1;
+    if (kernel == 2 && vec != 16) return fail(KVMIG_EINVAL, "the bulk-copy kernel needs 16-byte aligned runs; this shape gives %d", vec);
+    const int64_t stages = std::min<int64_t>(std::max<int64_t>(g_opt.stages.load(), 2), kMaxStages);
+    size_t smem = 0;
+    int64_t ctas_per_sm = g_opt.ctas_per_sm.load();
+    if (kernel == 2) {
+        smem = (size_t)stages * chunk + (size_t)stages * (8 + 8 + 4) + 16;
+        if ((int64_t)smem > st.max_smem_optin) return fail(KVMIG_ELIMIT, "stages x chunk_bytes exceeds the shared memory a CTA may use");
+        if (ctas_per_sm <= 0) {
+            const int64_t ring = stages * chunk, target = 72 * 1024;
+            ctas_per_sm = std::max<int64_t>(1, std::min<int64_t>(8, (target + ring - 1) / ring));
+            ctas_per_sm = std::min<int64_t>(ctas_per_sm, std::max<int64_t>(1, (220 * 1024) / (int64_t)(smem + 1024)));
+        }
+        if ((int)smem > st.bulk_smem_set) {
+            CU_TRY(cudaFuncSetAttribute(kv_migrate_bulk, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            st.bulk_smem_set = (int)smem;
+        }
+    } else if (ctas_per_sm <= 0) {
+        ctas_per_sm = 8;
+    }
+
+    // One upload carries the cleared status words and both tables: the array keeps whatever the last
+    // call left in it, so everything this launch reads is rewritten first.
+    const size_t words = (size_t)kStaticStatusWords + 2 * (size_t)n_ctx;
+    std::memset(g_static_stage, 0, kStaticStatusWords * sizeof(int));
+    for (int64_t i = 0; i < n_ctx; ++i) {
+        g_static_stage[kStaticStatusWords + i] = (int)ctx_blocks[i];
+        g_static_stage[kStaticStatusWords + n_ctx + i] = (int)dec_blocks[i];
+    }
+    CU_TRY(cudaMemcpyAsync(scratch, g_static_stage, words * sizeof(int), cudaMemcpyHostToDevice, stream));
+    g_cnt.memcpy_calls++;
+    p.src_ids = scratch + kStaticStatusWords;
+    p.dst_ids = scratch + kStaticStatusWords + n_ctx;
+    p.status = scratch;
+    p.n_blocks = (unsigned)n_ctx;
+    p.units_per_block = upb;
+    p.chunk_bytes = (unsigned)chunk;
+    p.total_units = (unsigned)(n_ctx * upb);
+    const unsigned grid = (unsigned)std::min<int64_t>(p.total_units, (int64_t)st.sm_count * ctas_per_sm);
+    cudaError_t e;
+    if (kernel == 2) {
+        kv_migrate_bulk<<<grid, 32, smem, stream>>>(p, (unsigned)stages, (unsigned)chunk);
+        e = cudaGetLastError();
+    } else {
+        switch (vec) {
+            case 16: e = launch_vec<16>(p, grid, stream); break;
+            case 8: e = launch_vec<8>(p, grid, stream); break;
+            case 4: e = launch_vec<4>(p, grid, stream); break;
+            case 2: e = launch_vec<2>(p, grid, stream); break;
+            default: e = launch_vec<1>(p, grid, stream); break;
+        }
+    }
+    if (e != cudaSuccess) return fail(KVMIG_ECUDA, "launching the migration kernel: %s", cudaGetErrorString(e));
+    g_cnt.kernel_launches++;
+    int status[4] = {0, 0, 0, 0};
+    CU_TRY(cudaMemcpyAsync(status, scratch, sizeof status, cudaMemcpyDeviceToHost, stream));
+    CU_TRY(cudaStreamSynchronize(stream));   // sources are read and the staging image is free again
+    if (status[0] != kDevOk)
+        return fail(KVMIG_EDEVICE, "migration kernel gave up (code %d) at work unit %d, detail %d", status[0], status[1], status[2]);
+    g_cnt.bytes_migrated += bytes_per_block * n_ctx;
+    return 0;
+}
+
 }  // namespace kvmig
 
 using namespace kvmig;
@@ -820,7 +1019,13 @@ int kvmig_register_ipc_mem_handle(const int64_t* k_handle, int64_t k_len, const 
     bool needed = false;
     for (const SegPlan& sp : plan)
         if (!(sp.ctx < key) && !(key < sp.ctx)) needed = true;
-    if (needed) {
+    auto prev = stp->registry.find(key);
+    if (prev != stp->registry.end() && prev->second.mapped && prev->second.hk == ce.hk && prev->second.hv == ce.hv) {
+        // The same pools registered again (by another decoding rank of this process): keep the mapping.
+        ce.k = prev->second.k;
+        ce.v = prev->second.v;
+        ce.mapped = true;
+    } else if (needed) {
         rc = map_pool(*stp, dev, ce.hk.data(), &ce.k);
         if (rc) return rc;
         rc = map_pool(*stp, dev, ce.hv.data(), &ce.v);
@@ -850,6 +1055,13 @@ int kvmig_migrate_blocks(int64_t ctx_pp, int64_t ctx_tp, const int64_t* ctx_bloc
                                k_cache, v_cache, shape, static_cast<cudaStream_t>(stream), &ticket);
     if (rc) return rc;
     return wait_ticket(ticket);
+}
+
+int kvmig_migrate_blocks_static(int64_t ctx_pp, int64_t ctx_tp, const int64_t* ctx_blocks, int64_t n_ctx, int64_t dec_pp,
+                                int64_t dec_tp, int64_t dec_pp_rank, int64_t dec_tp_rank, const int64_t* dec_blocks,
+                                int64_t n_dec, void* k_cache, void* v_cache, const kvmig_pool_shape* shape, void* stream) {
+    return migrate_static(ctx_pp, ctx_tp, ctx_blocks, n_ctx, dec_pp, dec_tp, dec_pp_rank, dec_tp_rank, dec_blocks, n_dec,
+                          k_cache, v_cache, shape, static_cast<cudaStream_t>(stream));
 }
 
 int kvmig_swap(const int64_t* src_ids, int64_t n_src, const int64_t* dst_ids, int64_t n_dst, int is_swap_in, void* k_cache,

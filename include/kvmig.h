@@ -135,6 +135,48 @@ KVMIG_API int kvmig_migrate_blocks_async(int64_t ctx_pp_size, int64_t ctx_tp_siz
 KVMIG_API int kvmig_migrate_wait(uint64_t ticket);
 
 /*
+ * kvmig_migrate_blocks for hosts that must not allocate.  (No counterpart in
+ * the reference: its worker has the one migrate operator.)
+ *
+ * The ordinary entry point keeps its block tables and status word in memory
+ * it obtains from cudaMalloc / cudaHostAlloc on first use.  A decoding worker
+ * that has sized its KV pools to take the HBM that was free at start-up
+ * (distserve/worker.py:152-192) cannot count on a later allocation
+ * succeeding, and an allocation in the middle of a decode loop can stall the
+ * device; other embedders simply forbid allocation after start-up.  This
+ * variant performs the same copy with the same kernels, arguments and
+ * completion rule (it returns when the source blocks have been read), but its
+ * scratch is a fixed array compiled into the library (33 KiB of device memory
+ * on every GPU that loads it, held until the process exits), and it calls no
+ * cudaMalloc, cudaFree, cudaHostAlloc, event creation or other allocating
+ * routine.
+ *
+ * Limits and rules:
+ *  - at most KVMIG_STATIC_MAX_BLOCKS block indexes per call; more is refused
+ *    with KVMIG_ELIMIT (split the lists, or use kvmig_migrate_blocks);
+ *  - every context worker it reads must already have been mapped by
+ *    kvmig_register_ipc_mem_handle for this decoding rank (mapping a peer pool
+ *    is registration's job; this call refuses instead of mapping);
+ *  - the first call on each device looks up the array's device address
+ *    (with that device current); make that first call before any stream
+ *    capture begins;
+ *  - all calls on a device share the one array, which keeps the previous
+ *    call's contents; each call rewrites every word it will read before it
+ *    launches.  Two calls whose kernels overlapped on the GPU would race on
+ *    the tables; the entry point therefore serialises its callers and returns
+ *    only after its kernel has finished, so calls made through it never
+ *    overlap.  Do not copy the pattern into an asynchronous wrapper.
+ */
+#define KVMIG_STATIC_MAX_BLOCKS 4096
+KVMIG_API int kvmig_migrate_blocks_static(int64_t ctx_pp_size, int64_t ctx_tp_size,
+                                const int64_t* ctx_blocks, int64_t num_ctx_blocks,
+                                int64_t dec_pp_size, int64_t dec_tp_size,
+                                int64_t dec_pp_rank, int64_t dec_tp_rank,
+                                const int64_t* dec_blocks, int64_t num_dec_blocks,
+                                void* k_cache, void* v_cache, const kvmig_pool_shape* shape,
+                                void* stream);
+
+/*
  * Copy whole blocks between the GPU pools and the pinned host pools, in list
  * order, on `stream`, without waiting for completion.  Replaces
  * torch.ops.swapping_ops.swap(source_block_ids, target_block_ids, is_swap_in,
