@@ -62,9 +62,11 @@ def parse_args():
     ap.add_argument("--chunk-bytes", type=int, default=None)
     ap.add_argument("--stages", type=int, default=None)
     ap.add_argument("--ctas-per-sm", type=int, default=None)
+    ap.add_argument("--opt", action="append", default=[], metavar="NAME=VALUE", help="any kvmig_set_option pair")
     ap.add_argument("--cpu-seconds", type=float, default=12.0, help="budget of the CPU baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-swap", action="store_true")
     return ap.parse_args()
 
 
@@ -138,32 +140,6 @@ class ClockSampler:
                     reasons.add(name)
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(smax) if smax else None,
                 "samples": len(sm), "samples_inside_timed_region": len(inside), "reasons": sorted(reasons)}
-
-
-def plan_roles(workload, world):
-    """rank -> ("ctx"|"dec", pp_rank, tp_rank, replica).  With one GPU both stages live on it."""
-    w = workload
-    n_ctx, n_dec = w.ctx_tp * w.ctx_pp, w.dec_tp * w.dec_pp
-    if world == 1:
-        return None
-    if world < n_ctx + n_dec:
-        raise SystemExit(f"workload {w.name} needs {n_ctx + n_dec} GPUs, got {world}")
-    roles = {}
-    r = 0
-    for p in range(w.ctx_pp):
-        for t in range(w.ctx_tp):
-            roles[r] = ("ctx", p, t, 0)
-            r += 1
-    replica = 0
-    while r + n_dec <= world:
-        for p in range(w.dec_pp):
-            for t in range(w.dec_tp):
-                roles[r] = ("dec", p, t, replica)
-                r += 1
-        replica += 1
-    for idle in range(r, world):
-        roles[idle] = ("idle", 0, 0, 0)
-    return roles
 
 
 def cpu_baseline(workload, trace, same_device: bool, seconds: float):
@@ -289,6 +265,10 @@ def main():
         if v is not None:
             capi.set_option(opt, v)
 
+    for pair in args.opt:
+        k, v = pair.split("=")
+        capi.set_option(k, int(v))
+
     dist = None
     if world > 1:
         import torch.distributed as dist
@@ -299,10 +279,12 @@ def main():
         if dist is not None:
             dist.barrier()
 
-    roles = plan_roles(w, world)
+    from distserve_b200.launch import Role, exchange_handles, num_replicas, plan_roles, shard_trace
+
+    roles = None if world == 1 else plan_roles(w, world)
     cache = CacheConfig(w.block_size, 1 << 20)
     ctx_worker = dec_worker = None
-    role = ("both", 0, 0, 0) if roles is None else roles[rank]
+    role = Role("both") if roles is None else roles[rank]
 
     def fill(worker):
         g = torch.Generator(device="cuda").manual_seed(w.seed * 1000 + rank)
@@ -310,13 +292,13 @@ def main():
             pool.normal_(generator=g)
 
     handles = None
-    if role[0] in ("ctx", "both"):
-        pc = w.ctx_config(role[1], role[2])
+    if role.stage in ("ctx", "both"):
+        pc = w.ctx_config(role.pp_rank, role.tp_rank)
         ctx_worker = KVWorker(rank, "context", w.model, cache, pc, device=local_rank)
         handles = ctx_worker.init_kvcache_and_swap(w.ctx_pool_blocks, 1)
         fill(ctx_worker)
-    if role[0] in ("dec", "both"):
-        pc = w.dec_config(role[1], role[2])
+    if role.stage in ("dec", "both"):
+        pc = w.dec_config(role.pp_rank, role.tp_rank)
         dec_worker = KVWorker(rank, "decoding", w.model, cache, pc, device=local_rank)
         dec_worker.init_kvcache_and_swap(w.dec_pool_blocks, 1)
         dec_worker.k_cache.zero_()
@@ -324,19 +306,13 @@ def main():
     torch.cuda.synchronize()
 
     # handle table [pp][tp] of the context stage, gathered the way the engine gathers it
-    if dist is None:
-        table = [[handles]]
-    else:
-        gathered = [None] * world
-        dist.all_gather_object(gathered, handles)
-        table = [[gathered[r] for r in sorted(roles) if roles[r][0] == "ctx" and roles[r][1] == p]
-                 for p in range(w.ctx_pp)]
+    table = [[handles]] if dist is None else exchange_handles(w, roles, handles)
     ctx_pc = w.ctx_config()
-    n_replicas = 1 if roles is None else max(1, len({v[3] for v in roles.values() if v[0] == "dec"}))
+    n_replicas = 1 if roles is None else num_replicas(roles)
     my_trace = []
     if dec_worker is not None:
         dec_worker.register_kvcache_mem_handles(ctx_pc, table)
-        my_trace = [t for i, t in enumerate(trace) if i % n_replicas == role[3]]
+        my_trace = list(trace) if roles is None else shard_trace(trace, role, n_replicas)
     barrier()
 
     stream = torch.cuda.current_stream()
@@ -388,7 +364,7 @@ def main():
         return ms
 
     sampler = ClockSampler(local_rank)
-    if rank == 0 or (roles is not None and roles[rank][0] == "dec" and roles[rank][3] == 0 and roles[rank][1:3] == (0, 0)):
+    if rank == 0 or (roles is not None and roles[rank] == Role("dec", 0, 0, 0)):
         sampler.start()
     for _ in range(args.warmup):
         if dec_worker is not None:
@@ -421,6 +397,34 @@ def main():
         if not verified:
             raise SystemExit("bench: migrated blocks differ from their sources")
 
+    # block swap (decoding stage only): scattered GPU blocks <-> pinned host blocks through the worker's protocol
+    swap_info = None
+    if same_device and dec_worker is not None and not args.no_swap:
+        n_swap = min(64, w.dec_pool_blocks)
+        dtype = dec_worker.k_cache.dtype
+        dec_worker.k_swap = torch.empty((n_swap,) + tuple(dec_worker.k_cache.shape[1:]), dtype=dtype, pin_memory=True)
+        dec_worker.v_swap = torch.empty_like(dec_worker.k_swap).pin_memory()
+        gpu_ids = [int(x) for x in torch.randperm(w.dec_pool_blocks)[:n_swap]]
+        host_ids = [int(x) for x in torch.randperm(n_swap)]
+        swap_bytes = n_swap * bytes_per_block
+        res = {}
+        for direction, is_in in (("out", False), ("in", True)):
+            times = []
+            for _ in range(4):
+                torch.cuda.synchronize()
+                t0 = time.perf_counter()
+                if is_in:
+                    dec_worker.swap_blocks([0], host_ids, gpu_ids, True)
+                    dec_worker.wait_for_all_swap_in()
+                else:
+                    dec_worker.swap_blocks([0], gpu_ids, host_ids, False)
+                    dec_worker.wait_for_all_swap_out()
+                times.append(time.perf_counter() - t0)
+            res[direction] = swap_bytes / min(times[1:]) / 1e9
+        swap_info = {"out_GBps": res["out"], "in_GBps": res["in"], "blocks": n_swap, "bytes_per_direction": swap_bytes,
+                     "api": "KVWorker.swap_blocks -> torch.ops.swapping_ops.swap, scattered ids, pinned host pool, "
+                            "best of 3 after warm-up, wall clock around enqueue + flush"}
+
     # aggregate over ranks
     totals = torch.tensor([float(my_bytes_per_step), float(launches), float(dec_worker is not None)], dtype=torch.float64)
     kern_ms = sum(e0.elapsed_time(e1) for e0, e1, _ in per_launch)
@@ -444,7 +448,7 @@ def main():
     if dist is not None:
         clk = [None] * world
         dist.all_gather_object(clk, clocks)
-        dec_clk = [c for r, c in enumerate(clk) if c and roles[r][0] == "dec" and c.get("sm_mhz")]
+        dec_clk = [c for r, c in enumerate(clk) if c and roles[r].stage == "dec" and c.get("sm_mhz")]
         if dec_clk:
             clocks = dec_clk[0]
 
@@ -485,7 +489,8 @@ def main():
         "frac_of_nvlink_900_per_dest": None if same_device else value / max(1, n_dest) / NVLINK_NOMINAL_GBS,
         "p50_migrate_latency_ms": p50.item() * 1e3 if lat or dist is not None else None,
         "roofline": roof, "gpu_launches": int(totals[1].item()), "clocks": clocks, "verified_on_device": verified,
-        "options": {k: capi.get_option(k) for k in ("kernel", "chunk_bytes", "stages", "ctas_per_sm")},
+        "options": {k: capi.get_option(k) for k in ("kernel", "chunk_bytes", "stages", "ctas_per_sm", "inline_tables",
+                                                   "overlap_launches")},
     }
     if e2e_value is not None:
         n_calls = len(trace) * n_dest // max(1, n_replicas) if not same_device else len(trace)
@@ -493,6 +498,8 @@ def main():
                        "h2d_bytes_per_step": 8 * trace_blocks(trace) * (n_dest // max(1, n_replicas) if not same_device else 1),
                        "d2h_bytes_per_step": 16 * n_calls,
                        "api": "torch.ops.block_migration_ops.migrate_blocks, one awaited call per request"}
+    if swap_info is not None:
+        line["swap"] = swap_info
     if not args.no_cpu_baseline and args.gpus == 1:
         line["cpu_baseline"] = cpu_baseline(w, trace, same_device, args.cpu_seconds)
     print(json.dumps(line))

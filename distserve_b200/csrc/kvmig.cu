@@ -61,6 +61,7 @@ struct MigParams {
     const int* dst_ids;
     int* status;                      // [0] code, [1] unit, [2] detail; host-mapped
     unsigned int nseg, n_blocks, units_per_block, total_units, chunk_bytes;
+    unsigned int wait_prior;          // 1: order this grid after the previous grid of the stream before touching memory
 };
 
 enum DevStatus { kDevOk = 0, kDevLoadTimeout = 1, kDevDrainTimeout = 2 };
@@ -71,7 +72,7 @@ struct Unit {
     unsigned int bytes;
 };
 
-__device__ __forceinline__ Unit decode_unit(const MigParams& p, unsigned int u) {
+__device__ __forceinline__ Unit decode_unit(const MigParams& p, const int* src_ids, const int* dst_ids, unsigned int u) {
     unsigned int blk = u / p.units_per_block;
     unsigned int r = u - blk * p.units_per_block;
     unsigned int si = 0;
@@ -84,8 +85,8 @@ __device__ __forceinline__ Unit decode_unit(const MigParams& p, unsigned int u) 
     unsigned long long rem = g.run_bytes - off;
     Unit out;
     out.bytes = rem < p.chunk_bytes ? (unsigned int)rem : p.chunk_bytes;
-    out.src = g.src + (unsigned long long)p.src_ids[blk] * g.src_block_stride + row * g.src_row_stride + off;
-    out.dst = g.dst + (unsigned long long)p.dst_ids[blk] * g.dst_block_stride + row * g.dst_row_stride + off;
+    out.src = g.src + (unsigned long long)src_ids[blk] * g.src_block_stride + row * g.src_row_stride + off;
+    out.dst = g.dst + (unsigned long long)dst_ids[blk] * g.dst_block_stride + row * g.dst_row_stride + off;
     return out;
 }
 
@@ -110,7 +111,7 @@ template <int VEC>
 __global__ void __launch_bounds__(kVecThreads) kv_migrate_vec(const __grid_constant__ MigParams p) {
     using T = typename VecType<VEC>::T;
     for (unsigned int u = blockIdx.x; u < p.total_units; u += gridDim.x) {
-        Unit w = decode_unit(p, u);
+        Unit w = decode_unit(p, p.src_ids, p.dst_ids, u);
         const T* s = reinterpret_cast<const T*>(w.src);
         T* d = reinterpret_cast<T*>(w.dst);
         unsigned int n = w.bytes / VEC;
@@ -175,8 +176,8 @@ __device__ __forceinline__ void fence_async_proxy() { asm volatile("fence.proxy.
 constexpr int kMaxStages = 16;
 
 // Shared memory: [stages * stage_bytes ring][stages mbarriers][stages dst ptr][stages sizes]
-__global__ void __launch_bounds__(32) kv_migrate_bulk(const __grid_constant__ MigParams p,
-                                                       unsigned int stages, unsigned int stage_bytes) {
+__device__ __forceinline__ void bulk_pipeline(const MigParams& p, const int* src_ids, const int* dst_ids,
+                                              unsigned int stages, unsigned int stage_bytes) {
     extern __shared__ __align__(128) unsigned char smem[];
     if (threadIdx.x != 0) return;
     unsigned char* ring = smem;
@@ -184,16 +185,20 @@ __global__ void __launch_bounds__(32) kv_migrate_bulk(const __grid_constant__ Mi
     char** dst_of = reinterpret_cast<char**>(bars + stages);
     unsigned int* bytes_of = reinterpret_cast<unsigned int*>(dst_of + stages);
 
+    // Let the next migration grid of the stream start while this one is still running (its ramp-up
+    // then hides this grid's tail).  The host sets wait_prior when the two grids are not independent.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     for (unsigned int s = 0; s < stages; ++s) mbar_init(&bars[s], 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     fence_async_proxy();
+    if (p.wait_prior) asm volatile("griddepcontrol.wait;" ::: "memory");
 
     const unsigned int first = blockIdx.x, stride = gridDim.x;
     const unsigned int mine = first < p.total_units ? (p.total_units - first + stride - 1) / stride : 0;
 
     auto issue_load = [&](unsigned int k) {
         unsigned int s = k % stages;
-        Unit w = decode_unit(p, first + k * stride);
+        Unit w = decode_unit(p, src_ids, dst_ids, first + k * stride);
         dst_of[s] = w.dst;
         bytes_of[s] = w.bytes;
         mbar_expect_tx(&bars[s], w.bytes);
@@ -231,6 +236,27 @@ __global__ void __launch_bounds__(32) kv_migrate_bulk(const __grid_constant__ Mi
             if (!mbar_wait_bounded(&bars[k % stages], (k / stages) & 1u)) { p.status[2] = kDevDrainTimeout; break; }
     }
     bulk_wait_all();
+}
+
+// Block tables in device memory (any number of blocks).
+__global__ void __launch_bounds__(32) kv_migrate_bulk(const __grid_constant__ MigParams p,
+                                                       unsigned int stages, unsigned int stage_bytes) {
+    bulk_pipeline(p, p.src_ids, p.dst_ids, stages, stage_bytes);
+}
+
+// Block tables carried in the kernel's own parameter block ([src ids | dst ids], n_blocks each):
+// a typical request (<= 256 blocks) then needs no table upload ahead of the launch, which removes a
+// copy-engine hop from the latency of every call.
+template <int NIDS>
+struct MigParamsInline {
+    MigParams base;
+    int ids[2 * NIDS];
+};
+
+template <int NIDS>
+__global__ void __launch_bounds__(32) kv_migrate_bulk_inline(const __grid_constant__ MigParamsInline<NIDS> q,
+                                                              unsigned int stages, unsigned int stage_bytes) {
+    bulk_pipeline(q.base, q.ids, q.ids + q.base.n_blocks, stages, stage_bytes);
 }
 
 // ---------------------------------------------------------------------------
@@ -277,7 +303,7 @@ int64_t handle_checksum(const int64_t* w) {
 // 3-stage ring and 3 CTAs per SM keep about 72 KiB in flight per SM, where HBM throughput
 // peaks; more bytes in flight lowered it again.
 struct Options {
-    std::atomic<int64_t> kernel{0}, chunk_bytes{8192}, stages{3}, ctas_per_sm{0};
+    std::atomic<int64_t> kernel{0}, chunk_bytes{8192}, stages{3}, ctas_per_sm{0}, inline_tables{1}, overlap_launches{1};
 };
 Options g_opt;
 
@@ -324,6 +350,9 @@ struct DeviceState {
     int sticky_error = 0;
     std::string sticky_text;
     int bulk_smem_set = 0;
+    // Per destination pool (keyed by the K pool's address): ticket sequence of the last launch that wrote
+    // each block, used to decide whether a new launch may overlap the launches still in flight.
+    std::map<const void*, std::vector<uint64_t>> last_writer;
 };
 
 std::mutex g_mu;
@@ -499,6 +528,37 @@ int pick_vec(uintptr_t bits) {
     return 1;
 }
 
+constexpr int kInlineSmall = 256;    // block ids per table that fit the classic 4 KB parameter block
+constexpr int kInlineLarge = 1024;   // needs the large (32 KB) parameter block of recent drivers
+
+template <int NIDS>
+cudaError_t launch_bulk_inline(const MigParams& p, const int64_t* src, const int64_t* dst, unsigned grid, size_t smem,
+                               cudaStream_t stream, int64_t stages, int64_t chunk, bool overlap) {
+    static_assert(sizeof(MigParamsInline<kInlineSmall>) <= 4096, "small inline tables must fit 4 KB of parameters");
+    MigParamsInline<NIDS> q;
+    q.base = p;
+    q.base.src_ids = q.base.dst_ids = nullptr;
+    const unsigned n = p.n_blocks;
+    for (unsigned i = 0; i < n; ++i) {
+        q.ids[i] = (int)src[i];
+        q.ids[n + i] = (int)dst[i];
+    }
+    // Programmatic stream serialization: this grid may begin once the previous grid of the stream has
+    // executed griddepcontrol.launch_dependents (our own kernels do so at once; any other kernel
+    // triggers only by finishing, which leaves ordinary stream order in place).
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(32);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = overlap ? 1 : 0;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kv_migrate_bulk_inline<NIDS>, q, (unsigned)stages, (unsigned)chunk);
+}
+
 template <int VEC>
 cudaError_t launch_vec(const MigParams& p, unsigned grid, cudaStream_t stream) {
     kv_migrate_vec<VEC><<<grid, kVecThreads, 0, stream>>>(p);
@@ -619,6 +679,10 @@ int enqueue_migration(int64_t ctx_pp, int64_t ctx_tp, const int64_t* ctx_blocks,
         }
         if ((int)smem > st.bulk_smem_set) {
             CU_TRY(cudaFuncSetAttribute(kv_migrate_bulk, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            CU_TRY(cudaFuncSetAttribute(kv_migrate_bulk_inline<kInlineSmall>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        (int)smem));
+            CU_TRY(cudaFuncSetAttribute(kv_migrate_bulk_inline<kInlineLarge>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        (int)smem));
             st.bulk_smem_set = (int)smem;
         }
     } else if (ctas_per_sm <= 0) {
@@ -630,15 +694,35 @@ int enqueue_migration(int64_t ctx_pp, int64_t ctx_tp, const int64_t* ctx_blocks,
     Slot& sl = st.slots[seq % KVMIG_MAX_INFLIGHT];
     rc = retire_slot(st, sl);
     if (rc && !st.sticky_error) { st.sticky_error = rc; st.sticky_text = g_err; }
-    rc = grow_slot(sl, n_ctx);
+    // Tables of a typical request ride in the kernel parameters; longer lists go through device memory.
+    const bool inline_tables = kernel == 2 && g_opt.inline_tables.load() != 0 && n_ctx <= kInlineLarge;
+    rc = grow_slot(sl, inline_tables ? 0 : n_ctx);
     if (rc) return rc;
-    for (int64_t i = 0; i < n_ctx; ++i) {
-        sl.h_tab[i] = (int)ctx_blocks[i];
-        sl.h_tab[n_ctx + i] = (int)dec_blocks[i];
-    }
     sl.status[0] = sl.status[1] = sl.status[2] = sl.status[3] = 0;
-    CU_TRY(cudaMemcpyAsync(sl.d_tab, sl.h_tab, 2 * n_ctx * sizeof(int), cudaMemcpyHostToDevice, stream));
-    g_cnt.memcpy_calls++;
+    // May this launch overlap the migrations still in flight?  Only if it writes none of their blocks.
+    const bool overlap = inline_tables && g_opt.overlap_launches.load() != 0;
+    bool depends = !overlap;
+    {
+        std::vector<uint64_t>& marks = st.last_writer[k_cache];
+        if ((int64_t)marks.size() < shape->num_blocks) marks.resize((size_t)shape->num_blocks, 0);
+        for (int64_t i = 0; i < n_ctx; ++i) {
+            uint64_t& m = marks[(size_t)dec_blocks[i]];
+            if (m != 0 && !depends) {
+                Slot& other = st.slots[m % KVMIG_MAX_INFLIGHT];
+                if (other.seq == m && other.busy && cudaEventQuery(other.done) != cudaSuccess) depends = true;
+            }
+            m = seq;
+        }
+        (void)cudaGetLastError();   // cudaEventQuery reports "not ready" through the error state
+    }
+    if (!inline_tables) {
+        for (int64_t i = 0; i < n_ctx; ++i) {
+            sl.h_tab[i] = (int)ctx_blocks[i];
+            sl.h_tab[n_ctx + i] = (int)dec_blocks[i];
+        }
+        CU_TRY(cudaMemcpyAsync(sl.d_tab, sl.h_tab, 2 * n_ctx * sizeof(int), cudaMemcpyHostToDevice, stream));
+        g_cnt.memcpy_calls++;
+    }
 
     int64_t bytes_per_block = 0;
     for (size_t s0 = 0; s0 < segs.size(); s0 += kMaxSegs) {
@@ -661,6 +745,7 @@ int enqueue_migration(int64_t ctx_pp, int64_t ctx_tp, const int64_t* ctx_blocks,
         p.n_blocks = (unsigned)n_ctx;
         p.units_per_block = upb;
         p.chunk_bytes = (unsigned)chunk;
+        p.wait_prior = depends ? 1u : 0u;
         // total_units is 32-bit: walk the block list in slices if a launch would overflow.
         const int64_t max_blocks = std::max<int64_t>(1, (int64_t)0x7fffffff / upb);
         for (int64_t b0 = 0; b0 < n_ctx; b0 += max_blocks) {
@@ -671,7 +756,13 @@ int enqueue_migration(int64_t ctx_pp, int64_t ctx_tp, const int64_t* ctx_blocks,
             p.total_units = (unsigned)(nb * upb);
             unsigned grid = (unsigned)std::min<int64_t>(p.total_units, (int64_t)st.sm_count * ctas_per_sm);
             cudaError_t e;
-            if (kernel == 2) {
+            if (inline_tables) {
+                e = n_ctx <= kInlineSmall
+                        ? launch_bulk_inline<kInlineSmall>(p, ctx_blocks + b0, dec_blocks + b0, grid, smem, stream, stages, chunk,
+                                                           overlap)
+                        : launch_bulk_inline<kInlineLarge>(p, ctx_blocks + b0, dec_blocks + b0, grid, smem, stream, stages,
+                                                           chunk, overlap);
+            } else if (kernel == 2) {
                 kv_migrate_bulk<<<grid, 32, smem, stream>>>(p, (unsigned)stages, (unsigned)chunk);
                 e = cudaGetLastError();
             } else {
@@ -1111,6 +1202,8 @@ static std::atomic<int64_t>* option_slot(const char* name) {
     if (!std::strcmp(name, "chunk_bytes")) return &g_opt.chunk_bytes;
     if (!std::strcmp(name, "stages")) return &g_opt.stages;
     if (!std::strcmp(name, "ctas_per_sm")) return &g_opt.ctas_per_sm;
+    if (!std::strcmp(name, "inline_tables")) return &g_opt.inline_tables;
+    if (!std::strcmp(name, "overlap_launches")) return &g_opt.overlap_launches;
     return nullptr;
 }
 

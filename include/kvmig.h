@@ -196,7 +196,12 @@ KVMIG_API int kvmig_swap(const int64_t* source_block_ids, int64_t num_source,
 /*
  * Tuning and introspection (no counterpart in the reference).
  *   options : "kernel" 0 auto | 1 vector loads | 2 bulk-copy pipeline,
- *             "chunk_bytes", "stages", "ctas_per_sm", "swap_kernel" (0/1)
+ *             "chunk_bytes", "stages", "ctas_per_sm",
+ *             "inline_tables" 1 = lists of up to 1024 blocks travel in the
+ *             kernel parameters instead of a device table (default 1),
+ *             "overlap_launches" 1 = a migration whose target blocks are
+ *             disjoint from those of the migrations still in flight may start
+ *             before they finish (default 1)
  *   counters: "kernel_launches", "memcpy_calls", "bytes_migrated",
  *             "bytes_swapped", "mapped_peers"
  */

@@ -26,7 +26,8 @@ LAYOUTS = [
 @pytest.fixture(autouse=True)
 def fresh_library_state():
     capi.reset_registry()
-    saved = {k: capi.get_option(k) for k in ("kernel", "chunk_bytes", "stages", "ctas_per_sm")}
+    saved = {k: capi.get_option(k) for k in ("kernel", "chunk_bytes", "stages", "ctas_per_sm", "inline_tables",
+                                             "overlap_launches")}
     yield
     for k, v in saved.items():
         capi.set_option(k, v)
@@ -39,10 +40,11 @@ def ragged_lists(rng, n_src, n_dst, n):
     return src, dst
 
 
-@pytest.mark.parametrize("kernel", [1, 2], ids=["vec", "bulk"])
+@pytest.mark.parametrize("kernel,inline", [(1, 0), (2, 1), (2, 0)], ids=["vec", "bulk-inline-tables", "bulk-device-tables"])
 @pytest.mark.parametrize("L,H,ctx,dec", LAYOUTS)
-def test_layouts_match_oracle(L, H, ctx, dec, kernel):
+def test_layouts_match_oracle(L, H, ctx, dec, kernel, inline):
     capi.set_option("kernel", kernel)
+    capi.set_option("inline_tables", inline)
     rng = np.random.default_rng(L * 31 + H)
     B, D = 4, 16
     cs = Stage(L, H, ctx[0], ctx[1], 37, B, D, seed=1)
@@ -153,7 +155,7 @@ def test_many_blocks_in_one_call_and_table_growth():
     cs = Stage(2, 2, 1, 1, 6000, 2, 8, seed=12)
     ds = Stage(2, 2, 2, 1, 5000, 2, 8, seed=13)
     register_all(cs, ds)
-    for n in (3, 2500, 5000):
+    for n in (3, 256, 257, 1024, 1025, 2500, 5000):     # both inline-table sizes, then device tables
         src, dst = ragged_lists(rng, 6000, 5000, n)
         migrate_all(cs, ds, src, dst)
         oracle_all(cs, ds, src, dst)
@@ -179,6 +181,39 @@ def test_async_tickets():
     capi.migrate_wait(tickets[0])                         # waiting twice is harmless
     with pytest.raises(capi.KvmigError, match="unknown ticket"):
         capi.migrate_wait(tickets[-1] + 1000)
+    assert_stage_equals_host(ds)
+
+
+@pytest.mark.parametrize("overlap", [1, 0])
+def test_launches_that_share_target_blocks_keep_stream_order(overlap):
+    """Back-to-back launches may overlap on the GPU only when their target
+    blocks are disjoint.  Here every launch rewrites the same targets from
+    different sources (large enough that launches would still be running when
+    the next one is enqueued); the pools must end up as if run one by one."""
+    capi.set_option("overlap_launches", overlap)
+    rng = np.random.default_rng(18)
+    cs = Stage(8, 8, 1, 1, 256, 16, 64, seed=18)         # 256 KiB per block per pool
+    ds = Stage(8, 8, 1, 1, 64, 16, 64, seed=19)
+    register_all(cs, ds)
+    k, v = ds.dev[(0, 0)]
+    stream = torch.cuda.Stream()
+    tickets = []
+    targets = list(range(40))
+    for i in range(7):
+        src = [int(x) for x in rng.integers(0, 256, size=40)]
+        dst = targets if i % 2 == 0 else targets[::-1]
+        tickets.append(capi.migrate_blocks_async(1, 1, src, 1, 1, 0, 0, dst, k.data_ptr(), v.data_ptr(), ds.shape(),
+                                                 stream.cuda_stream))
+        oracle_all(cs, ds, src, dst)
+    # independent launches in between and after: disjoint targets
+    for i in range(3):
+        src = [int(x) for x in rng.integers(0, 256, size=8)]
+        dst = list(range(40 + 8 * i, 48 + 8 * i))
+        tickets.append(capi.migrate_blocks_async(1, 1, src, 1, 1, 0, 0, dst, k.data_ptr(), v.data_ptr(), ds.shape(),
+                                                 stream.cuda_stream))
+        oracle_all(cs, ds, src, dst)
+    for t in tickets:
+        capi.migrate_wait(t)
     assert_stage_equals_host(ds)
 
 
