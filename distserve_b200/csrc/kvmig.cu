@@ -303,7 +303,7 @@ int64_t handle_checksum(const int64_t* w) {
 // 3-stage ring and 3 CTAs per SM keep about 72 KiB in flight per SM, where HBM throughput
 // peaks; more bytes in flight lowered it again.
 struct Options {
-    std::atomic<int64_t> kernel{0}, chunk_bytes{8192}, stages{3}, ctas_per_sm{0}, inline_tables{1}, overlap_launches{1};
+    std::atomic<int64_t> kernel{0}, chunk_bytes{8192}, stages{3}, ctas_per_sm{0}, inline_tables{1}, overlap_launches{1}, max_ctas{0};
 };
 Options g_opt;
 
@@ -353,6 +353,7 @@ struct DeviceState {
     // Per destination pool (keyed by the K pool's address): ticket sequence of the last launch that wrote
     // each block, used to decide whether a new launch may overlap the launches still in flight.
     std::map<const void*, std::vector<uint64_t>> last_writer;
+    std::vector<char> seen;   // duplicate-target bitmap, all zero between calls
 };
 
 std::mutex g_mu;
@@ -642,20 +643,27 @@ int enqueue_migration(int64_t ctx_pp, int64_t ctx_tp, const int64_t* ctx_blocks,
         }
     }
 
-    // Validate ids before anything is enqueued.
-    std::vector<char> seen;
-    if (n_dec > 0) seen.assign((size_t)shape->num_blocks, 0);
-    for (int64_t i = 0; i < n_ctx; ++i) {
+    // Validate ids before anything is enqueued.  `seen` is a per-device bitmap kept all-zero between calls.
+    std::vector<char>& seen = st.seen;
+    if ((int64_t)seen.size() < shape->num_blocks) seen.resize((size_t)shape->num_blocks, 0);
+    int64_t checked = 0;
+    rc = 0;
+    for (; checked < n_ctx && !rc; ++checked) {
+        const int64_t i = checked;
         if (ctx_blocks[i] < 0 || ctx_blocks[i] >= src_num_blocks)
-            return fail(KVMIG_EINVAL, "context_block_indexes[%lld] = %lld is outside the context pool (%lld blocks)", (long long)i,
-                        (long long)ctx_blocks[i], (long long)src_num_blocks);
-        if (dec_blocks[i] < 0 || dec_blocks[i] >= shape->num_blocks)
-            return fail(KVMIG_EINVAL, "decoding_block_indexes[%lld] = %lld is outside the decoding pool (%lld blocks)",
-                        (long long)i, (long long)dec_blocks[i], (long long)shape->num_blocks);
-        if (seen[(size_t)dec_blocks[i]])
-            return fail(KVMIG_EINVAL, "decoding_block_indexes names block %lld twice", (long long)dec_blocks[i]);
-        seen[(size_t)dec_blocks[i]] = 1;
+            rc = fail(KVMIG_EINVAL, "context_block_indexes[%lld] = %lld is outside the context pool (%lld blocks)", (long long)i,
+                      (long long)ctx_blocks[i], (long long)src_num_blocks);
+        else if (dec_blocks[i] < 0 || dec_blocks[i] >= shape->num_blocks)
+            rc = fail(KVMIG_EINVAL, "decoding_block_indexes[%lld] = %lld is outside the decoding pool (%lld blocks)",
+                      (long long)i, (long long)dec_blocks[i], (long long)shape->num_blocks);
+        else if (seen[(size_t)dec_blocks[i]])
+            rc = fail(KVMIG_EINVAL, "decoding_block_indexes names block %lld twice", (long long)dec_blocks[i]);
+        else
+            seen[(size_t)dec_blocks[i]] = 1;
     }
+    for (int64_t i = 0; i < checked; ++i)
+        if (dec_blocks[i] >= 0 && dec_blocks[i] < shape->num_blocks) seen[(size_t)dec_blocks[i]] = 0;
+    if (rc) return rc;
     if (n_ctx == 0) return 0;
 
     // Kernel choice.
@@ -705,11 +713,17 @@ int enqueue_migration(int64_t ctx_pp, int64_t ctx_tp, const int64_t* ctx_blocks,
     {
         std::vector<uint64_t>& marks = st.last_writer[k_cache];
         if ((int64_t)marks.size() < shape->num_blocks) marks.resize((size_t)shape->num_blocks, 0);
+        int running[KVMIG_MAX_INFLIGHT];   // -1 unknown, 0 finished, 1 still running; one query per slot at most
+        for (int& r : running) r = -1;
         for (int64_t i = 0; i < n_ctx; ++i) {
             uint64_t& m = marks[(size_t)dec_blocks[i]];
             if (m != 0 && !depends) {
-                Slot& other = st.slots[m % KVMIG_MAX_INFLIGHT];
-                if (other.seq == m && other.busy && cudaEventQuery(other.done) != cudaSuccess) depends = true;
+                const int si = (int)(m % KVMIG_MAX_INFLIGHT);
+                Slot& other = st.slots[si];
+                if (other.seq == m && other.busy) {
+                    if (running[si] < 0) running[si] = cudaEventQuery(other.done) == cudaSuccess ? 0 : 1;
+                    if (running[si] == 1) depends = true;
+                }
             }
             m = seq;
         }
@@ -755,6 +769,8 @@ int enqueue_migration(int64_t ctx_pp, int64_t ctx_tp, const int64_t* ctx_blocks,
             p.n_blocks = (unsigned)nb;
             p.total_units = (unsigned)(nb * upb);
             unsigned grid = (unsigned)std::min<int64_t>(p.total_units, (int64_t)st.sm_count * ctas_per_sm);
+            // A cap on the grid leaves whole SMs to a decode step running beside the migration.
+            if (const int64_t cap = g_opt.max_ctas.load(); cap > 0) grid = (unsigned)std::min<int64_t>(grid, cap);
             cudaError_t e;
             if (inline_tables) {
                 e = n_ctx <= kInlineSmall
@@ -1204,6 +1220,7 @@ static std::atomic<int64_t>* option_slot(const char* name) {
     if (!std::strcmp(name, "ctas_per_sm")) return &g_opt.ctas_per_sm;
     if (!std::strcmp(name, "inline_tables")) return &g_opt.inline_tables;
     if (!std::strcmp(name, "overlap_launches")) return &g_opt.overlap_launches;
+    if (!std::strcmp(name, "max_ctas")) return &g_opt.max_ctas;
     return nullptr;
 }
 

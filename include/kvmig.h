@@ -201,7 +201,10 @@ KVMIG_API int kvmig_swap(const int64_t* source_block_ids, int64_t num_source,
  *             kernel parameters instead of a device table (default 1),
  *             "overlap_launches" 1 = a migration whose target blocks are
  *             disjoint from those of the migrations still in flight may start
- *             before they finish (default 1)
+ *             before they finish (default 1),
+ *             "max_ctas" N > 0 = launch at most N CTAs, so that a migration
+ *             running beside a decode step leaves the other SMs to it
+ *             (default 0 = no cap)
  *   counters: "kernel_launches", "memcpy_calls", "bytes_migrated",
  *             "bytes_swapped", "mapped_peers"
  */

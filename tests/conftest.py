@@ -23,3 +23,13 @@ def built_libs():
 @pytest.fixture(scope="session")
 def golden_dir():
     return ROOT / "tests" / "golden"
+
+
+@pytest.fixture(autouse=True)
+def _first_device_is_current():
+    """GPU tests assume cuda:0 is the current device unless they say otherwise."""
+    import torch
+
+    if torch.cuda.is_available():
+        torch.cuda.set_device(0)
+    yield
