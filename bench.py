@@ -9,8 +9,10 @@ regions of K steps each follow W warm-up steps:
 
 * ``value`` — requests enqueued back to back through the asynchronous C-ABI
   entry point; KV pools resident in HBM; timed with CUDA events on the
-  launching stream.  Every kernel launch is bracketed by its own pair of events
-  for the roofline figure.
+  launching stream around the whole region.  The launches run back to back on
+  that stream, so the roofline figure uses region time / launches as the
+  average launch duration (an event between launches would serialise launches
+  that the library lets overlap).
 * ``e2e``   — the call a DistServe worker makes: ``torch.ops.block_migration_ops
   .migrate_blocks`` with Python block-index lists, returning only when the
   source blocks may be recycled.  The host->device traffic of this path is the
@@ -198,6 +200,7 @@ def cpu_baseline(workload, trace, same_device: bool, seconds: float):
             break
     dt_s = time.perf_counter() - t0
     return {"value": factor * moved / dt_s / 1e9, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
+            "ms_per_sample_pass": dt_s * 1e3 / passes,
             "sample": f"first {len(sample)} requests of {w.name}, ids folded into {max_pool}-block host pools, "
                       f"{passes} passes in {dt_s:.1f} s, torch index_select/index_copy_ on {torch.get_num_threads()} threads"}
 
@@ -240,7 +243,7 @@ def main():
             return
         base = cpu_baseline(w, trace, same_device, max(args.cpu_seconds, 5.0) * max(1, min(args.steps, 3)))
         line = {"impl": "reference", "metric": METRIC, "value": base["value"], "unit": UNIT, "n_gpus": args.gpus,
-                "steps": args.steps, "warmup": args.warmup, "ms_per_step": None, "higher_is_better": True,
+                "steps": args.steps, "warmup": args.warmup, "ms_per_step": base["ms_per_sample_pass"], "higher_is_better": True,
                 "scaling": "weak", "vs_baseline": None, "dtype": "u16 (fp16 payload moved as bytes)", "data": "synthetic",
                 "config": config, "cpu_baseline": base,
                 "e2e": {"value": base["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -322,20 +325,12 @@ def main():
     my_bytes_per_step = sum(len(t.src_blocks) for t in my_trace) * bytes_per_block
     factor = 2 if same_device else 1
 
-    def step_async(record=None):
-        tickets = []
-        for item in my_trace:
-            if record is not None:
-                e0 = torch.cuda.Event(enable_timing=True)
-                e0.record(stream)
-            tickets.append(capi.migrate_blocks_async(
-                ctx_pc.pipeline_parallel_size, ctx_pc.tensor_parallel_size, item.src_blocks,
-                pc.pipeline_parallel_size, pc.tensor_parallel_size, pc.pipeline_parallel_rank, pc.tensor_parallel_rank,
-                item.dst_blocks, dec_worker.k_cache.data_ptr(), dec_worker.v_cache.data_ptr(), shape, stream.cuda_stream))
-            if record is not None:
-                e1 = torch.cuda.Event(enable_timing=True)
-                e1.record(stream)
-                record.append((e0, e1, len(item.src_blocks) * bytes_per_block))
+    def step_async():
+        tickets = [capi.migrate_blocks_async(
+            ctx_pc.pipeline_parallel_size, ctx_pc.tensor_parallel_size, item.src_blocks,
+            pc.pipeline_parallel_size, pc.tensor_parallel_size, pc.pipeline_parallel_rank, pc.tensor_parallel_rank,
+            item.dst_blocks, dec_worker.k_cache.data_ptr(), dec_worker.v_cache.data_ptr(), shape, stream.cuda_stream)
+            for item in my_trace]
         for t in tickets:
             capi.migrate_wait(t)
 
@@ -347,7 +342,9 @@ def main():
                 latencies.append(time.perf_counter() - t0)
 
     def timed(step_fn, steps, **kw):
-        """K steps between barriers; device time by CUDA events on the launching stream, max over ranks."""
+        """K steps between barriers; device time by CUDA events on the launching stream.  Returns the
+        max over ranks and this rank's own time.  No event is recorded between launches: a timing event
+        there would serialise launches that the library lets overlap."""
         barrier()
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record(stream)
@@ -356,12 +353,13 @@ def main():
                 step_fn(**kw)
         b.record(stream)
         barrier()
-        ms = a.elapsed_time(b)
+        mine = a.elapsed_time(b)
+        ms = mine
         if dist is not None:
             t = torch.tensor([ms], dtype=torch.float64)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             ms = float(t.item())
-        return ms
+        return ms, mine
 
     sampler = ClockSampler(local_rank)
     if rank == 0 or (roles is not None and roles[rank] == Role("dec", 0, 0, 0)):
@@ -373,11 +371,11 @@ def main():
                 step_e2e()
     sampler.mark(0)
     launches0 = capi.get_counter("kernel_launches")
-    per_launch = []
-    ms_value = timed(step_async, args.steps, record=per_launch)
-    launches = capi.get_counter("kernel_launches") - launches0
+    ms_value, my_ms_value = timed(step_async, args.steps)
+    value_launches = capi.get_counter("kernel_launches") - launches0
     latencies = []
-    ms_e2e = None if args.no_e2e else timed(step_e2e, args.steps, latencies=latencies)
+    ms_e2e = None if args.no_e2e else timed(step_e2e, args.steps, latencies=latencies)[0]
+    launches = capi.get_counter("kernel_launches") - launches0
     sampler.mark(1)
     clocks = sampler.stop() if sampler.proc is not None or rank == 0 else None
 
@@ -427,9 +425,9 @@ def main():
 
     # aggregate over ranks
     totals = torch.tensor([float(my_bytes_per_step), float(launches), float(dec_worker is not None)], dtype=torch.float64)
-    kern_ms = sum(e0.elapsed_time(e1) for e0, e1, _ in per_launch)
-    kern_bytes = sum(b for _, _, b in per_launch)
-    kern = torch.tensor([kern_ms, float(kern_bytes), float(len(per_launch))], dtype=torch.float64)
+    # launches of the `value` region run back to back on one stream: average launch duration = region / launches
+    kern = torch.tensor([my_ms_value if dec_worker is not None else 0.0, float(my_bytes_per_step * args.steps),
+                         float(value_launches)], dtype=torch.float64)
     lat = sorted(latencies)
     p50 = torch.tensor([lat[len(lat) // 2] if lat else 0.0], dtype=torch.float64)
     if dist is not None:
