@@ -244,7 +244,7 @@ def main():
         base = cpu_baseline(w, trace, same_device, max(args.cpu_seconds, 5.0) * max(1, min(args.steps, 3)))
         line = {"impl": "reference", "metric": METRIC, "value": base["value"], "unit": UNIT, "n_gpus": args.gpus,
                 "steps": args.steps, "warmup": args.warmup, "ms_per_step": base["ms_per_sample_pass"], "higher_is_better": True,
-                "scaling": "weak", "vs_baseline": None, "dtype": "u16 (fp16 payload moved as bytes)", "data": "synthetic",
+                "scaling": "weak", "vs_baseline": None, "dtype": "u8", "data": "synthetic",
                 "config": config, "cpu_baseline": base,
                 "e2e": {"value": base["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
                 "note": "the reference's native copy (SwiftTransformer) is not in its tree; this arm is the CPU "
@@ -482,7 +482,7 @@ def main():
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms_value / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "u16 (fp16 payload moved as bytes)", "data": "synthetic", "config": config,
+        "dtype": "u8", "data": "synthetic", "config": config,
         "per_dest_gpu_GBps": value / max(1, n_dest), "dest_gpus": n_dest,
         "frac_of_nvlink_900_per_dest": None if same_device else value / max(1, n_dest) / NVLINK_NOMINAL_GBS,
         "p50_migrate_latency_ms": p50.item() * 1e3 if lat or dist is not None else None,

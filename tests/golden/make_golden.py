@@ -278,7 +278,7 @@ def golden_worker_calls(tmp: str):
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    ref_root = sys.argv[1] if len(sys.argv) > 1 else str(ROOT.parent / "reference")   # a checkout beside this repo
     import_reference(ref_root)
     with tempfile.TemporaryDirectory() as tmp:
         for name, fn in (("geometry", golden_geometry), ("block_manager", golden_block_manager),

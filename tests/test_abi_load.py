@@ -108,7 +108,7 @@ def test_shim_registers_the_reference_operator_names(built_libs):
         torch.ops.block_migration_ops.register_ipc_mem_handle([1], [2], 4, 4, [1, 0, 1, 0], [1, 0, 1, 0])
 
 
-REFERENCE = Path("/root/reference")
+REFERENCE = Path(os.environ.get("DISTSERVE_REFERENCE_DIR", ROOT.parent / "reference"))   # a checkout beside this repo
 
 
 @pytest.mark.skipif(not (REFERENCE / "distserve").is_dir(), reason="reference checkout not present")
