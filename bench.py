@@ -461,6 +461,12 @@ def main():
             gbs = factor * k_bytes / (k_ms / 1e3) / 1e9
             if worst is None or gbs < worst[0]:
                 worst = (gbs, k_ms / k_n, k_bytes / k_n)
+    if capi.get_option("kernel") == 1:
+        kernel_label = "kv_migrate_vec<16>"
+    elif capi.get_option("inline_tables") and max(len(t.src_blocks) for t in trace) <= 256:
+        kernel_label = "kv_migrate_bulk_inline<256>"
+    else:
+        kernel_label = "kv_migrate_bulk / kv_migrate_bulk_inline"
     if same_device:
         peak, peak_kind = hbm_peak()
         # ncu on a small case of this kernel (profiles/): DRAM reads equal the algorithmic read bytes, DRAM
@@ -470,14 +476,14 @@ def main():
         roof = {"bound": "hbm", "achieved": worst[0], "peak": peak, "unit": "GB/s", "frac": worst[0] / peak,
                 "traffic": traffic, "peak_source": f"{peak_kind} copy bandwidth (MEASURED_PEAKS.json)" if peak_kind == "measured"
                 else "fallback 6650 GB/s", "avg_launch_us": worst[1] * 1e3, "algorithmic_bytes_per_launch": factor * worst[2],
-                "kernel": "kv_migrate_bulk" if capi.get_option("kernel") in (0, 2) else "kv_migrate_vec"}
+                "kernel": kernel_label}
     else:
         roof = {"bound": "nvlink", "achieved": worst[0], "peak": NVLINK_NOMINAL_GBS, "unit": "GB/s",
                 "frac": worst[0] / NVLINK_NOMINAL_GBS, "traffic": None,
                 "peak_source": "nominal NVLink 5 ingress per GPU per direction",
                 "frac_of_measured_p2p_770": worst[0] / NVLINK_MEASURED_P2P_GBS, "avg_launch_us": worst[1] * 1e3,
                 "algorithmic_bytes_per_launch": worst[2], "per": "slowest destination GPU",
-                "kernel": "kv_migrate_bulk" if capi.get_option("kernel") in (0, 2) else "kv_migrate_vec"}
+                "kernel": kernel_label}
 
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
