@@ -48,6 +48,9 @@ SIGNATURES = {
     "kvmig_migrate_blocks_async": (C.c_int, [C.c_int64, C.c_int64, _I64P, C.c_int64, C.c_int64, C.c_int64, C.c_int64,
                                              C.c_int64, _I64P, C.c_int64, C.c_void_p, C.c_void_p, _SHAPEP, C.c_void_p,
                                              C.POINTER(C.c_uint64)]),
+    "kvmig_migrate_layers_async": (C.c_int, [C.c_int64, C.c_int64, _I64P, C.c_int64, C.c_int64, C.c_int64, C.c_int64,
+                                             C.c_int64, _I64P, C.c_int64, C.c_void_p, C.c_void_p, _SHAPEP, C.c_int64,
+                                             C.c_int64, C.c_void_p, C.POINTER(C.c_uint64)]),
     "kvmig_migrate_wait": (C.c_int, [C.c_uint64]),
     "kvmig_migrate_blocks_static": (C.c_int, [C.c_int64, C.c_int64, _I64P, C.c_int64, C.c_int64, C.c_int64, C.c_int64,
                                               C.c_int64, _I64P, C.c_int64, C.c_void_p, C.c_void_p, _SHAPEP, C.c_void_p]),
@@ -127,6 +130,16 @@ def migrate_blocks_async(ctx_pp, ctx_tp, ctx_blocks, dec_pp, dec_tp, dec_pp_rank
     _check(lib().kvmig_migrate_blocks_async(ctx_pp, ctx_tp, _i64(ctx_blocks), len(ctx_blocks), dec_pp, dec_tp,
                                             dec_pp_rank, dec_tp_rank, _i64(dec_blocks), len(dec_blocks), k_ptr, v_ptr,
                                             C.byref(shape), stream, C.byref(ticket)))
+    return ticket.value
+
+
+def migrate_layers_async(ctx_pp, ctx_tp, ctx_blocks, dec_pp, dec_tp, dec_pp_rank, dec_tp_rank, dec_blocks,
+                         k_ptr: int, v_ptr: int, shape: PoolShape, layer_begin: int, layer_end: int, stream: int = 0) -> int:
+    """Enqueue the copy of the global layers [layer_begin, layer_end) only; returns a ticket."""
+    ticket = C.c_uint64(0)
+    _check(lib().kvmig_migrate_layers_async(ctx_pp, ctx_tp, _i64(ctx_blocks), len(ctx_blocks), dec_pp, dec_tp,
+                                            dec_pp_rank, dec_tp_rank, _i64(dec_blocks), len(dec_blocks), k_ptr, v_ptr,
+                                            C.byref(shape), layer_begin, layer_end, stream, C.byref(ticket)))
     return ticket.value
 
 

@@ -278,6 +278,9 @@ __device__ __forceinline__ void bulk_pipeline(const MigParams& p, const int* src
             if (!mbar_wait_bounded(&bars[k % stages], (k / stages) & 1u)) { p.status[2] = kDevDrainTimeout; break; }
     }
     bulk_wait_all();
+    // A grid that was allowed to start before its predecessor finished must not *finish* before it: whatever
+    // follows in the stream waits only for this grid, and must thereby have waited for every earlier one.
+    if (!p.wait_prior) asm volatile("griddepcontrol.wait;" ::: "memory");
     if (work) {
         // The last CTA to finish rearms the counter pair for the next launch that uses it.
         __threadfence();
@@ -387,6 +390,7 @@ struct Slot {
     int* status = nullptr;     // pinned + mapped, 4 ints
     int* status_dev = nullptr;
     int* work = nullptr;       // kWorkPairs counter pairs in device memory, zero whenever no launch is using them
+    int64_t layer0 = 0, layer1 = INT64_MAX;   // window of global layers the launch in flight writes
     cudaEvent_t done = nullptr;
     int64_t cap = 0;           // ids per table
     uint64_t seq = 0;          // ticket sequence currently (or last) using this slot
@@ -629,7 +633,8 @@ cudaError_t launch_vec(const MigParams& p, unsigned grid, cudaStream_t stream) {
 
 int enqueue_migration(int64_t ctx_pp, int64_t ctx_tp, const int64_t* ctx_blocks, int64_t n_ctx, int64_t dec_pp,
                       int64_t dec_tp, int64_t dec_pp_rank, int64_t dec_tp_rank, const int64_t* dec_blocks, int64_t n_dec,
-                      void* k_cache, void* v_cache, const kvmig_pool_shape* shape, cudaStream_t stream, uint64_t* ticket) {
+                      void* k_cache, void* v_cache, const kvmig_pool_shape* shape, cudaStream_t stream, uint64_t* ticket,
+                      int64_t layer_begin = 0, int64_t layer_end = INT64_MAX) {
     g_err.clear();
     if (ticket) *ticket = 0;
     int rc = check_shape(shape, "migrate_blocks");
@@ -652,6 +657,25 @@ int enqueue_migration(int64_t ctx_pp, int64_t ctx_tp, const int64_t* ctx_blocks,
     std::vector<SegPlan> plan;
     rc = plan_segments(L, H, ctx_tp, ctx_pp, dec_tp, dec_tp_rank, dec_pp, dec_pp_rank, &plan);
     if (rc) return rc;
+    // Optional window of global layers: keep only the part of each segment that lies inside it.
+    if (layer_begin < 0 || layer_end < layer_begin)
+        return fail(KVMIG_EINVAL, "layer window [%lld, %lld) is not a range", (long long)layer_begin, (long long)layer_end);
+    layer_end = std::min(layer_end, L);
+    const bool windowed = layer_begin > 0 || layer_end < L;
+    if (windowed) {
+        const int64_t first_layer = dec_pp_rank * shape->num_layers;   // global index of this worker's local layer 0
+        std::vector<SegPlan> clipped;
+        for (SegPlan sp : plan) {
+            const int64_t g0 = first_layer + sp.dst_layer_off, g1 = g0 + sp.n_layers;
+            const int64_t a = std::max(g0, layer_begin), b = std::min(g1, layer_end);
+            if (a >= b) continue;
+            sp.src_layer_off += a - g0;
+            sp.dst_layer_off += a - g0;
+            sp.n_layers = b - a;
+            clipped.push_back(sp);
+        }
+        plan.swap(clipped);
+    }
 
     const int64_t slab = shape->block_size * shape->head_dim * shape->elem_size;
     const int64_t Lc = L / ctx_pp, Hc = H / ctx_tp;
@@ -725,7 +749,7 @@ int enqueue_migration(int64_t ctx_pp, int64_t ctx_tp, const int64_t* ctx_blocks,
     for (int64_t i = 0; i < checked; ++i)
         if (dec_blocks[i] >= 0 && dec_blocks[i] < shape->num_blocks) seen[(size_t)dec_blocks[i]] = 0;
     if (rc) return rc;
-    if (n_ctx == 0) return 0;
+    if (n_ctx == 0 || plan.empty()) return 0;   // nothing to move (empty lists, or the window misses this worker)
 
     // Kernel choice.
     const int vec = pick_vec(align_bits);
@@ -781,7 +805,7 @@ int enqueue_migration(int64_t ctx_pp, int64_t ctx_tp, const int64_t* ctx_blocks,
             if (m != 0 && !depends) {
                 const int si = (int)(m % KVMIG_MAX_INFLIGHT);
                 Slot& other = st.slots[si];
-                if (other.seq == m && other.busy) {
+                if (other.seq == m && other.busy && other.layer0 < layer_end && layer_begin < other.layer1) {
                     if (running[si] < 0) running[si] = cudaEventQuery(other.done) == cudaSuccess ? 0 : 1;
                     if (running[si] == 1) depends = true;
                 }
@@ -869,6 +893,8 @@ int enqueue_migration(int64_t ctx_pp, int64_t ctx_tp, const int64_t* ctx_blocks,
     CU_TRY(cudaEventRecord(sl.done, stream));
     sl.busy = true;
     sl.seq = seq;
+    sl.layer0 = layer_begin;
+    sl.layer1 = layer_end;
     sl.bytes = bytes_per_block * n_ctx;
     if (ticket) *ticket = ((uint64_t)(unsigned)dev << 48) | seq;
     return 0;
@@ -879,14 +905,23 @@ int wait_ticket(uint64_t ticket) {
     if (ticket == 0) return 0;
     int dev = (int)(ticket >> 48);
     uint64_t seq = ticket & ((1ULL << 48) - 1);
-    std::lock_guard<std::mutex> lock(g_mu);
+    std::unique_lock<std::mutex> lock(g_mu);
     auto it = g_dev.find(dev);
     if (it == g_dev.end()) return fail(KVMIG_EINVAL, "unknown ticket");
-    DeviceState& st = it->second;
+    DeviceState& st = it->second;      // std::map nodes stay put, so the reference survives unlocking
     if (seq >= st.next_seq) return fail(KVMIG_EINVAL, "unknown ticket");
     Slot& sl = st.slots[seq % KVMIG_MAX_INFLIGHT];
     int rc = 0;
-    if (sl.seq == seq) rc = retire_slot(st, sl);
+    if (sl.seq == seq && sl.busy) {
+        // Wait for the kernel without holding the lock, so other threads can keep enqueuing; the event
+        // stays valid (events are created once per slot and never destroyed).
+        cudaEvent_t done = sl.done;
+        lock.unlock();
+        cudaError_t e = cudaEventSynchronize(done);
+        lock.lock();
+        if (e != cudaSuccess) rc = fail(KVMIG_ECUDA, "waiting for the migration kernel: %s", cudaGetErrorString(e));
+        if (!rc && sl.seq == seq) rc = retire_slot(st, sl);   // returns at once: the event has completed
+    }
     if (!rc && st.sticky_error) {
         rc = st.sticky_error;
         g_err = st.sticky_text;
@@ -1222,6 +1257,15 @@ int kvmig_migrate_blocks_async(int64_t ctx_pp, int64_t ctx_tp, const int64_t* ct
     if (!ticket) return fail(KVMIG_EINVAL, "ticket is NULL");
     return enqueue_migration(ctx_pp, ctx_tp, ctx_blocks, n_ctx, dec_pp, dec_tp, dec_pp_rank, dec_tp_rank, dec_blocks, n_dec,
                              k_cache, v_cache, shape, static_cast<cudaStream_t>(stream), ticket);
+}
+
+int kvmig_migrate_layers_async(int64_t ctx_pp, int64_t ctx_tp, const int64_t* ctx_blocks, int64_t n_ctx, int64_t dec_pp,
+                               int64_t dec_tp, int64_t dec_pp_rank, int64_t dec_tp_rank, const int64_t* dec_blocks,
+                               int64_t n_dec, void* k_cache, void* v_cache, const kvmig_pool_shape* shape,
+                               int64_t layer_begin, int64_t layer_end, void* stream, uint64_t* ticket) {
+    if (!ticket) return fail(KVMIG_EINVAL, "ticket is NULL");
+    return enqueue_migration(ctx_pp, ctx_tp, ctx_blocks, n_ctx, dec_pp, dec_tp, dec_pp_rank, dec_tp_rank, dec_blocks, n_dec,
+                             k_cache, v_cache, shape, static_cast<cudaStream_t>(stream), ticket, layer_begin, layer_end);
 }
 
 int kvmig_migrate_wait(uint64_t ticket) { return wait_ticket(ticket); }

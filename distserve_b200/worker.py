@@ -122,6 +122,20 @@ class KVWorker:
                 pc.pipeline_parallel_rank, pc.tensor_parallel_rank, decoding_block_indexes,
                 self.k_cache.data_ptr(), self.v_cache.data_ptr(), self._pool_shape(), s.cuda_stream)
 
+    def migrate_layers_async(self, context_block_indexes: List[int], context_parallel_config: ParallelConfig,
+                             decoding_block_indexes: List[int], layer_begin: int, layer_end: int,
+                             stream: Optional[torch.cuda.Stream] = None) -> int:
+        """Enqueue the copy of the global layers [layer_begin, layer_end) only (the part this worker
+        holds), for a context stage that releases a request's KV layer by layer while prefill runs."""
+        with torch.cuda.device(self.device):
+            s = stream if stream is not None else torch.cuda.current_stream()
+            pc = self.parallel_config
+            return capi.migrate_layers_async(
+                context_parallel_config.pipeline_parallel_size, context_parallel_config.tensor_parallel_size,
+                context_block_indexes, pc.pipeline_parallel_size, pc.tensor_parallel_size,
+                pc.pipeline_parallel_rank, pc.tensor_parallel_rank, decoding_block_indexes,
+                self.k_cache.data_ptr(), self.v_cache.data_ptr(), self._pool_shape(), layer_begin, layer_end, s.cuda_stream)
+
     def migrate_wait(self, ticket: int) -> None:
         capi.migrate_wait(ticket)
 

@@ -135,6 +135,26 @@ KVMIG_API int kvmig_migrate_blocks_async(int64_t ctx_pp_size, int64_t ctx_tp_siz
 KVMIG_API int kvmig_migrate_wait(uint64_t ticket);
 
 /*
+ * kvmig_migrate_blocks_async restricted to the global layers
+ * [layer_begin, layer_end): only the part of this worker's rectangle inside
+ * the window is copied (nothing, and no launch, if the window misses the
+ * worker's layers).  The reference migrates a request only after its whole
+ * prefill has finished (distserve/single_stage_engine.py:393-401); with this
+ * call a context stage that signals per-layer completion can have the
+ * decoding stage pull each group of layers while prefill is still computing
+ * the next ones.  Launches whose windows are disjoint may overlap on the GPU
+ * even when they write the same blocks.
+ */
+KVMIG_API int kvmig_migrate_layers_async(int64_t ctx_pp_size, int64_t ctx_tp_size,
+                               const int64_t* ctx_blocks, int64_t num_ctx_blocks,
+                               int64_t dec_pp_size, int64_t dec_tp_size,
+                               int64_t dec_pp_rank, int64_t dec_tp_rank,
+                               const int64_t* dec_blocks, int64_t num_dec_blocks,
+                               void* k_cache, void* v_cache, const kvmig_pool_shape* shape,
+                               int64_t layer_begin, int64_t layer_end,
+                               void* stream, uint64_t* ticket);
+
+/*
  * kvmig_migrate_blocks for hosts that must not allocate.  (No counterpart in
  * the reference: its worker has the one migrate operator.)
  *

@@ -246,3 +246,51 @@ def test_full_size_blocks_round_trip():
             pools["C"][x].zero_()
     assert inv is not None
     assert capi.get_counter("bytes_migrated") - before == 4 * nb * 2 * ps.block_bytes
+
+
+def test_layer_windows_compose_to_the_full_migration():
+    """Pulling a request layer group by layer group (out of order, on two
+    streams) must leave exactly what one full migration leaves; after the
+    first group only that group's layers may have changed."""
+    rng = np.random.default_rng(20)
+    L, H = 12, 4
+    cs = Stage(L, H, 2, 3, 30, 4, 16, seed=20)            # context tp=2, pp=3
+    ds = Stage(L, H, 1, 2, 26, 4, 16, seed=21)            # decoding tp=1, pp=2: worker p holds layers [6p, 6p+6)
+    register_all(cs, ds)
+    src, dst = ragged_lists(rng, 30, 26, 11)
+    before = {key: (k.clone(), v.clone()) for key, (k, v) in ds.dev.items()}
+    streams = [torch.cuda.Stream(), torch.cuda.Stream()]
+    windows = [(4, 9), (0, 4), (9, 12)]                    # the first one straddles both decoding workers
+    tickets = []
+
+    def pull(window, stream):
+        for dp in range(2):
+            k, v = ds.dev[(dp, 0)]
+            tickets.append(capi.migrate_layers_async(3, 2, src, 2, 1, dp, 0, dst, k.data_ptr(), v.data_ptr(), ds.shape((dp, 0)),
+                                                     window[0], window[1], stream.cuda_stream))
+
+    pull(windows[0], streams[0])
+    for t in tickets:
+        capi.migrate_wait(t)
+    oracle_all(cs, ds, src, dst)                           # host copies now hold the full result
+    for dp in range(2):
+        k, v = ds.dev[(dp, 0)]
+        lo, hi = max(4, 6 * dp) - 6 * dp, min(9, 6 * dp + 6) - 6 * dp
+        inside = list(range(lo, hi))
+        outside = [l for l in range(6) if l not in inside]
+        full_k = torch.from_numpy(ds.host[(dp, 0)][0]).cuda()
+        assert torch.equal(k[:, inside], full_k[:, inside])
+        assert torch.equal(k[:, outside], before[(dp, 0)][0][:, outside])
+    pull(windows[1], streams[1])
+    pull(windows[2], streams[0])
+    for t in tickets:
+        capi.migrate_wait(t)
+    assert_stage_equals_host(ds)
+    # a window that misses the worker launches nothing; a malformed one is refused
+    k, v = ds.dev[(0, 0)]
+    launches = capi.get_counter("kernel_launches")
+    t = capi.migrate_layers_async(3, 2, src, 2, 1, 0, 0, dst, k.data_ptr(), v.data_ptr(), ds.shape((0, 0)), 6, 12, 0)
+    capi.migrate_wait(t)
+    assert capi.get_counter("kernel_launches") == launches
+    with pytest.raises(capi.KvmigError, match="not a range"):
+        capi.migrate_layers_async(3, 2, src, 2, 1, 0, 0, dst, k.data_ptr(), v.data_ptr(), ds.shape((0, 0)), 5, 2, 0)
