@@ -294,3 +294,47 @@ def test_layer_windows_compose_to_the_full_migration():
     assert capi.get_counter("kernel_launches") == launches
     with pytest.raises(capi.KvmigError, match="not a range"):
         capi.migrate_layers_async(3, 2, src, 2, 1, 0, 0, dst, k.data_ptr(), v.data_ptr(), ds.shape((0, 0)), 5, 2, 0)
+
+
+def test_concurrent_host_threads():
+    """Two host threads, each with its own decoding pools and stream, enqueue
+    and await migrations at the same time (ctypes drops the GIL inside the
+    library); both must end bit-exact."""
+    import threading
+
+    cs = Stage(4, 4, 1, 1, 128, 8, 32, seed=30)
+    pools = [Stage(4, 4, 1, 1, 96, 8, 32, seed=31 + i) for i in range(2)]
+    register_all(cs, pools[0])
+    plans = []
+    for i, ds in enumerate(pools):
+        rng = np.random.default_rng(40 + i)
+        plan = [ragged_lists(rng, 128, 96, int(rng.integers(1, 40))) for _ in range(60)]
+        for src, dst in plan:
+            oracle_all(cs, ds, src, dst)
+        plans.append(plan)
+    errors = []
+
+    def worker(i):
+        try:
+            torch.cuda.set_device(0)
+            ds, stream = pools[i], torch.cuda.Stream()
+            k, v = ds.dev[(0, 0)]
+            for j, (src, dst) in enumerate(plans[i]):
+                if j % 3 == 0:
+                    capi.migrate_blocks(1, 1, src, 1, 1, 0, 0, dst, k.data_ptr(), v.data_ptr(), ds.shape(), stream.cuda_stream)
+                else:
+                    t = capi.migrate_blocks_async(1, 1, src, 1, 1, 0, 0, dst, k.data_ptr(), v.data_ptr(), ds.shape(),
+                                                  stream.cuda_stream)
+                    capi.migrate_wait(t)
+        except Exception as e:   # surfaced below
+            errors.append(e)
+
+    threads = [threading.Thread(target=worker, args=(i,)) for i in range(2)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join(120)
+    assert not errors, errors
+    torch.cuda.synchronize()
+    for ds in pools:
+        assert_stage_equals_host(ds)
