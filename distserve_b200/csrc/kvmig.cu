@@ -44,7 +44,7 @@ namespace kvmig {
 constexpr int kMaxSegs = 16;          // segments per launch (more -> several launches)
 constexpr int kVecThreads = 256;
 constexpr int kVecUnroll = 4;
-constexpr unsigned kSpinLimit = 1u << 22;  // bounded mbarrier polling (each poll may itself block briefly)
+constexpr unsigned kSpinLimit = 1u << 26;  // hard cap on mbarrier polls, on top of the time limit below
 
 struct __align__(16) Seg {
     const char* src;                  // context pool base + in-block offset of the rectangle
@@ -63,6 +63,8 @@ struct MigParams {
     unsigned int nseg, n_blocks, units_per_block, total_units, chunk_bytes;
     unsigned int wait_prior;          // 1: order this grid after the previous grid of the stream before touching memory
     unsigned int l2_hint;             // bit 0: loads evict-first in L2, bit 1: stores evict-first in L2
+    unsigned int lose_unit_plus1;     // diagnostic: unit (index + 1) whose load is armed but never issued; 0 = none
+    unsigned long long wait_limit_ns; // longest wait for one load before the kernel gives up
     unsigned int batch;               // units drawn per visit to the work counter
     int* work;                        // {next unit, finished CTAs}, both zero between launches; NULL = static deal
 };
@@ -154,10 +156,20 @@ __device__ __forceinline__ bool mbar_try_wait(unsigned long long* bar, unsigned 
         : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
     return ok != 0;
 }
-// Polls at most kSpinLimit times; false means the load never signalled.
-__device__ __forceinline__ bool mbar_wait_bounded(unsigned long long* bar, unsigned int parity) {
-    for (unsigned int it = 0; it < kSpinLimit; ++it)
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+// Waits for the barrier's phase, but never longer than limit_ns (nor more than kSpinLimit polls);
+// false means the load never signalled.
+__device__ __forceinline__ bool mbar_wait_bounded(unsigned long long* bar, unsigned int parity, unsigned long long limit_ns) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long t0 = global_ns();
+    for (unsigned int it = 0; it < kSpinLimit; ++it) {
         if (mbar_try_wait(bar, parity)) return true;
+        if ((it & 63u) == 63u && global_ns() - t0 > limit_ns) return false;
+    }
     return false;
 }
 __device__ __forceinline__ void bulk_g2s(void* smem_dst, const void* gsrc, unsigned int bytes, unsigned long long* bar) {
@@ -243,8 +255,14 @@ __device__ __forceinline__ void bulk_pipeline(const MigParams& p, const int* src
         dst_of[s] = w.dst;
         bytes_of[s] = w.bytes;
         mbar_expect_tx(&bars[s], w.bytes);
-        if (p.l2_hint & 1u) bulk_g2s_hint(ring + (size_t)s * stage_bytes, w.src, w.bytes, &bars[s], pol);
-        else bulk_g2s(ring + (size_t)s * stage_bytes, w.src, w.bytes, &bars[s]);
+        if (p.lose_unit_plus1 && u + 1u == p.lose_unit_plus1) {
+            // Failure-path exercise: the barrier is armed but the load is never issued, so the wait below
+            // must run out and report.  Nothing is in flight towards this stage, so leaving is safe.
+        } else if (p.l2_hint & 1u) {
+            bulk_g2s_hint(ring + (size_t)s * stage_bytes, w.src, w.bytes, &bars[s], pol);
+        } else {
+            bulk_g2s(ring + (size_t)s * stage_bytes, w.src, w.bytes, &bars[s]);
+        }
         ++issued;
     };
 
@@ -254,7 +272,7 @@ __device__ __forceinline__ void bulk_pipeline(const MigParams& p, const int* src
     bool ok = true;
     for (unsigned int k = 0; k < issued; ++k) {      // `issued` grows while units remain
         const unsigned int s = k % stages;
-        if (!mbar_wait_bounded(&bars[s], (k / stages) & 1u)) {
+        if (!mbar_wait_bounded(&bars[s], (k / stages) & 1u, p.wait_limit_ns)) {
             p.status[0] = kDevLoadTimeout;
             p.status[1] = (int)k;
             ok = false;
@@ -275,7 +293,7 @@ __device__ __forceinline__ void bulk_pipeline(const MigParams& p, const int* src
         // Give every load already in flight a bounded chance to land before the
         // shared memory it targets is released.
         for (unsigned int k = waited + 1; k < issued; ++k)
-            if (!mbar_wait_bounded(&bars[k % stages], (k / stages) & 1u)) { p.status[2] = kDevDrainTimeout; break; }
+            if (!mbar_wait_bounded(&bars[k % stages], (k / stages) & 1u, p.wait_limit_ns)) { p.status[2] = kDevDrainTimeout; break; }
     }
     bulk_wait_all();
     // A grid that was allowed to start before its predecessor finished must not *finish* before it: whatever
@@ -360,7 +378,7 @@ int64_t handle_checksum(const int64_t* w) {
 // SM upward saturates NVLink.
 struct Options {
     std::atomic<int64_t> kernel{0}, chunk_bytes{8192}, stages{3}, ctas_per_sm{0}, inline_tables{1}, overlap_launches{1}, max_ctas{0}, l2_hint{0},
-        dynamic_units{1};
+        dynamic_units{1}, wait_limit_ms{2000}, lose_unit_plus1{0};
 };
 Options g_opt;
 
@@ -847,6 +865,8 @@ int enqueue_migration(int64_t ctx_pp, int64_t ctx_tp, const int64_t* ctx_blocks,
         p.chunk_bytes = (unsigned)chunk;
         p.wait_prior = depends ? 1u : 0u;
         p.l2_hint = (unsigned)g_opt.l2_hint.load();
+        p.wait_limit_ns = (unsigned long long)std::max<int64_t>(1, g_opt.wait_limit_ms.load()) * 1000000ULL;
+        p.lose_unit_plus1 = (unsigned)g_opt.lose_unit_plus1.load();
         // total_units is 32-bit: walk the block list in slices if a launch would overflow.
         const int64_t max_blocks = std::max<int64_t>(1, (int64_t)0x7fffffff / upb);
         for (int64_t b0 = 0; b0 < n_ctx; b0 += max_blocks) {
@@ -1102,6 +1122,7 @@ int migrate_static(int64_t ctx_pp, int64_t ctx_tp, const int64_t* ctx_blocks, in
     p.status = scratch;
     p.n_blocks = (unsigned)n_ctx;
     p.units_per_block = upb;
+    p.wait_limit_ns = (unsigned long long)std::max<int64_t>(1, g_opt.wait_limit_ms.load()) * 1000000ULL;
     p.chunk_bytes = (unsigned)chunk;
     p.total_units = (unsigned)(n_ctx * upb);
     const unsigned grid = (unsigned)std::min<int64_t>(p.total_units, (int64_t)st.sm_count * ctas_per_sm);
@@ -1339,6 +1360,8 @@ static std::atomic<int64_t>* option_slot(const char* name) {
     if (!std::strcmp(name, "max_ctas")) return &g_opt.max_ctas;
     if (!std::strcmp(name, "l2_hint")) return &g_opt.l2_hint;
     if (!std::strcmp(name, "dynamic_units")) return &g_opt.dynamic_units;
+    if (!std::strcmp(name, "wait_limit_ms")) return &g_opt.wait_limit_ms;
+    if (!std::strcmp(name, "lose_unit_plus1")) return &g_opt.lose_unit_plus1;
     return nullptr;
 }
 

@@ -228,7 +228,13 @@ KVMIG_API int kvmig_swap(const int64_t* source_block_ids, int64_t num_source,
  *             "dynamic_units" 1 = CTAs draw work units from a device counter
  *             instead of a fixed round-robin share (default 1),
  *             "l2_hint" bit 0 / bit 1 = evict-first L2 policy on the bulk
- *             loads / stores (default 0)
+ *             loads / stores (default 0),
+ *             "wait_limit_ms" longest the copy kernel waits for one of its
+ *             loads before it records the failure and returns, making the
+ *             call fail with KVMIG_EDEVICE (default 2000),
+ *             "lose_unit_plus1" N > 0 = failure-path exercise: work unit N-1
+ *             arms its completion barrier but never issues its load, so that
+ *             wait runs out (default 0)
  *   counters: "kernel_launches", "memcpy_calls", "bytes_migrated",
  *             "bytes_swapped", "mapped_peers"
  */

@@ -338,3 +338,35 @@ def test_concurrent_host_threads():
     torch.cuda.synchronize()
     for ds in pools:
         assert_stage_equals_host(ds)
+
+
+def test_a_load_that_never_completes_is_reported_not_hung():
+    """Failure-path exercise without any fault: one work unit arms its
+    completion barrier but never issues its load.  The kernel's bounded wait
+    must run out, the call must fail with KVMIG_EDEVICE, and the library and
+    the CUDA context must stay usable."""
+    cs = Stage(4, 4, 1, 1, 16, 16, 64, seed=50)
+    ds = Stage(4, 4, 1, 1, 16, 16, 64, seed=51)
+    register_all(cs, ds)
+    src, dst = [3, 9, 1], [0, 5, 7]
+    saved = {k: capi.get_option(k) for k in ("wait_limit_ms", "lose_unit_plus1")}
+    try:
+        capi.set_option("wait_limit_ms", 30)
+        for entry in ("awaited", "ticket"):
+            capi.set_option("lose_unit_plus1", 2)
+            k, v = ds.dev[(0, 0)]
+            with pytest.raises(capi.KvmigError, match="gave up") as e:
+                if entry == "awaited":
+                    capi.migrate_blocks(1, 1, src, 1, 1, 0, 0, dst, k.data_ptr(), v.data_ptr(), ds.shape())
+                else:
+                    capi.migrate_wait(capi.migrate_blocks_async(1, 1, src, 1, 1, 0, 0, dst, k.data_ptr(), v.data_ptr(),
+                                                                ds.shape()))
+            assert e.value.code == capi.EDEVICE
+            capi.set_option("lose_unit_plus1", 0)
+            torch.cuda.synchronize()                      # the context is alive
+            migrate_all(cs, ds, src, dst)                 # and the same call now succeeds
+    finally:
+        for name, value in saved.items():
+            capi.set_option(name, value)
+    oracle_all(cs, ds, src, dst)
+    assert_stage_equals_host(ds)
