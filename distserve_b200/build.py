@@ -58,7 +58,7 @@ def build_kvmig(force: bool = False) -> Path:
     src = CSRC / "kvmig.cu"
     hdr = INCLUDE / "kvmig.h"
     LIB.mkdir(exist_ok=True)
-    if force or _stale(KVMIG_SO, [src, hdr]):
+    if force or _stale(KVMIG_SO, [src, hdr, CSRC / "kvmig_kernels.cuh"]):
         _run([_nvcc(), *NVCC_FLAGS, "-o", KVMIG_SO, src], "libkvmig.build.log")
     return KVMIG_SO
 

@@ -1,22 +1,20 @@
-// Paged-KV block migration and swap for B200 (sm_100a): copy kernels, the
-// per-process registry of mapped context-stage pools, and the C ABI declared
-// in include/kvmig.h.
+// Paged-KV block migration and swap for B200 (sm_100a): the per-process registry of mapped
+// context-stage pools, launch planning, and the C ABI declared in include/kvmig.h.  The kernels
+// live in kvmig_kernels.cuh.
 //
-// The data path is a pure byte move.  A decoding-stage worker pulls, for each
-// migrated block, the (layer range x KV-head range) rectangle it owns out of
-// the context-stage workers' pools.  Every such rectangle decomposes into
-// "segments" (one per contributing context worker and per K/V pool), each a
-// 2-D strided copy per block: `rows` runs of `run_bytes` contiguous bytes.
-// Runs are cut into chunks; one chunk is the unit of work a CTA takes from a
-// static round-robin schedule, so neighbouring CTAs touch neighbouring DRAM
-// pages.  Two kernels execute the same schedule:
-//   * kv_migrate_bulk : one elected thread per CTA drives a ring of shared
-//     memory stages with cp.async.bulk (global -> shared, completion on an
-//     mbarrier; shared -> global as a bulk group).  No multicast anywhere.
-//   * kv_migrate_vec  : 256 threads, 16-byte (or narrower, for odd shapes)
-//     vector loads and stores, four in flight per thread.
-// Source and destination block ids come from device-resident int32 tables
-// uploaded once per call.
+// The data path is a pure byte move.  A decoding-stage worker pulls, for each migrated block, the
+// (layer range x KV-head range) rectangle it owns out of the context-stage workers' pools.  The
+// host side
+//   * keeps, per device, the registered context workers and their mapped pool addresses
+//     (CUDA IPC for other processes, the raw address for pools of this process);
+//   * turns a call into segments (contributing context worker x K/V pool), validates the block
+//     lists, picks the kernel (bulk-copy pipeline when every run is 16-byte aligned, vector loads
+//     otherwise) and its grid;
+//   * hands out tickets backed by an event, a status word in mapped pinned memory and a pair of
+//     work counters per launch; block tables of up to 1024 blocks ride in the kernel parameters,
+//     longer ones go through a device table;
+//   * lets a migration start before earlier ones have finished when its target blocks are
+//     disjoint from theirs (programmatic dependent launch), and orders it after them otherwise.
 #include "../../include/kvmig.h"
 
 #include <cuda_runtime.h>
@@ -35,301 +33,9 @@
 #include <vector>
 #include <unistd.h>
 
+#include "kvmig_kernels.cuh"
+
 namespace kvmig {
-
-// ---------------------------------------------------------------------------
-// Device side
-// ---------------------------------------------------------------------------
-
-constexpr int kMaxSegs = 16;          // segments per launch (more -> several launches)
-constexpr int kVecThreads = 256;
-constexpr int kVecUnroll = 4;
-constexpr unsigned kSpinLimit = 1u << 26;  // hard cap on mbarrier polls, on top of the time limit below
-
-struct __align__(16) Seg {
-    const char* src;                  // context pool base + in-block offset of the rectangle
-    char* dst;                        // decoding pool base + in-block offset
-    unsigned long long src_block_stride, dst_block_stride;
-    unsigned long long src_row_stride, dst_row_stride;
-    unsigned long long run_bytes;
-    unsigned int rows, chunks_per_run, units_per_block, unit_begin;
-};
-
-struct MigParams {
-    Seg seg[kMaxSegs];
-    const int* src_ids;
-    const int* dst_ids;
-    int* status;                      // [0] code, [1] unit, [2] detail; host-mapped
-    unsigned int nseg, n_blocks, units_per_block, total_units, chunk_bytes;
-    unsigned int wait_prior;          // 1: order this grid after the previous grid of the stream before touching memory
-    unsigned int l2_hint;             // bit 0: loads evict-first in L2, bit 1: stores evict-first in L2
-    unsigned int lose_unit_plus1;     // diagnostic: unit (index + 1) whose load is armed but never issued; 0 = none
-    unsigned long long wait_limit_ns; // longest wait for one load before the kernel gives up
-    unsigned int batch;               // units drawn per visit to the work counter
-    int* work;                        // {next unit, finished CTAs}, both zero between launches; NULL = static deal
-};
-
-enum DevStatus { kDevOk = 0, kDevLoadTimeout = 1, kDevDrainTimeout = 2 };
-
-struct Unit {
-    const char* src;
-    char* dst;
-    unsigned int bytes;
-};
-
-__device__ __forceinline__ Unit decode_unit(const MigParams& p, const int* src_ids, const int* dst_ids, unsigned int u) {
-    unsigned int blk = u / p.units_per_block;
-    unsigned int r = u - blk * p.units_per_block;
-    unsigned int si = 0;
-    while (si + 1 < p.nseg && r >= p.seg[si + 1].unit_begin) ++si;
-    const Seg& g = p.seg[si];
-    r -= g.unit_begin;
-    unsigned int row = r / g.chunks_per_run;
-    unsigned int c = r - row * g.chunks_per_run;
-    unsigned long long off = (unsigned long long)c * p.chunk_bytes;
-    unsigned long long rem = g.run_bytes - off;
-    Unit out;
-    out.bytes = rem < p.chunk_bytes ? (unsigned int)rem : p.chunk_bytes;
-    out.src = g.src + (unsigned long long)src_ids[blk] * g.src_block_stride + row * g.src_row_stride + off;
-    out.dst = g.dst + (unsigned long long)dst_ids[blk] * g.dst_block_stride + row * g.dst_row_stride + off;
-    return out;
-}
-
-// ---- vector-load kernel ----------------------------------------------------
-
-template <int VEC> struct VecType;
-template <> struct VecType<16> { using T = uint4; };
-template <> struct VecType<8> { using T = uint2; };
-template <> struct VecType<4> { using T = unsigned int; };
-template <> struct VecType<2> { using T = unsigned short; };
-template <> struct VecType<1> { using T = unsigned char; };
-
-__device__ __forceinline__ uint4 ld_stream(const uint4* p) {
-    uint4 v;
-    asm volatile("ld.global.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
-    return v;
-}
-template <typename T> __device__ __forceinline__ T ld_stream(const T* p) { return *p; }
-
-template <int VEC>
-__global__ void __launch_bounds__(kVecThreads) kv_migrate_vec(const __grid_constant__ MigParams p) {
-    using T = typename VecType<VEC>::T;
-    for (unsigned int u = blockIdx.x; u < p.total_units; u += gridDim.x) {
-        Unit w = decode_unit(p, p.src_ids, p.dst_ids, u);
-        const T* s = reinterpret_cast<const T*>(w.src);
-        T* d = reinterpret_cast<T*>(w.dst);
-        unsigned int n = w.bytes / VEC;
-        for (unsigned int base = threadIdx.x; base < n; base += kVecThreads * kVecUnroll) {
-            T v[kVecUnroll];
-#pragma unroll
-            for (int j = 0; j < kVecUnroll; ++j) {
-                unsigned int i = base + j * kVecThreads;
-                if (i < n) v[j] = ld_stream(s + i);
-            }
-#pragma unroll
-            for (int j = 0; j < kVecUnroll; ++j) {
-                unsigned int i = base + j * kVecThreads;
-                if (i < n) d[i] = v[j];
-            }
-        }
-    }
-}
-
-// ---- bulk-copy (TMA, untiled) pipeline kernel ------------------------------
-
-__device__ __forceinline__ unsigned int smem_u32(const void* p) {
-    return (unsigned int)__cvta_generic_to_shared(p);
-}
-__device__ __forceinline__ void mbar_init(unsigned long long* bar, unsigned int count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(unsigned long long* bar, unsigned int bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(unsigned long long* bar, unsigned int parity) {
-    unsigned int ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
-    return ok != 0;
-}
-__device__ __forceinline__ unsigned long long global_ns() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-    return t;
-}
-// Waits for the barrier's phase, but never longer than limit_ns (nor more than kSpinLimit polls);
-// false means the load never signalled.
-__device__ __forceinline__ bool mbar_wait_bounded(unsigned long long* bar, unsigned int parity, unsigned long long limit_ns) {
-    if (mbar_try_wait(bar, parity)) return true;
-    const unsigned long long t0 = global_ns();
-    for (unsigned int it = 0; it < kSpinLimit; ++it) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if ((it & 63u) == 63u && global_ns() - t0 > limit_ns) return false;
-    }
-    return false;
-}
-__device__ __forceinline__ void bulk_g2s(void* smem_dst, const void* gsrc, unsigned int bytes, unsigned long long* bar) {
-    asm volatile(
-        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-        ::"r"(smem_u32(smem_dst)), "l"(gsrc), "r"(bytes), "r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void bulk_s2g(void* gdst, const void* smem_src, unsigned int bytes) {
-    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
-                 ::"l"(gdst), "r"(smem_u32(smem_src)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ unsigned long long l2_evict_first_policy() {
-    unsigned long long pol;
-    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
-    return pol;
-}
-__device__ __forceinline__ void bulk_g2s_hint(void* smem_dst, const void* gsrc, unsigned int bytes, unsigned long long* bar,
-                                              unsigned long long pol) {
-    asm volatile(
-        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;"
-        ::"r"(smem_u32(smem_dst)), "l"(gsrc), "r"(bytes), "r"(smem_u32(bar)), "l"(pol) : "memory");
-}
-__device__ __forceinline__ void bulk_s2g_hint(void* gdst, const void* smem_src, unsigned int bytes, unsigned long long pol) {
-    asm volatile("cp.async.bulk.global.shared::cta.bulk_group.L2::cache_hint [%0], [%1], %2, %3;"
-                 ::"l"(gdst), "r"(smem_u32(smem_src)), "r"(bytes), "l"(pol) : "memory");
-}
-__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
-template <int N> __device__ __forceinline__ void bulk_wait_read() {
-    asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
-}
-__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
-__device__ __forceinline__ void fence_async_proxy() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-
-constexpr int kMaxStages = 16;
-
-// Shared memory: [stages * stage_bytes ring][stages mbarriers][stages dst ptr][stages sizes]
-__device__ __forceinline__ void bulk_pipeline(const MigParams& p, const int* src_ids, const int* dst_ids,
-                                              unsigned int stages, unsigned int stage_bytes) {
-    extern __shared__ __align__(128) unsigned char smem[];
-    if (threadIdx.x != 0) return;
-    unsigned char* ring = smem;
-    unsigned long long* bars = reinterpret_cast<unsigned long long*>(smem + (size_t)stages * stage_bytes);
-    char** dst_of = reinterpret_cast<char**>(bars + stages);
-    unsigned int* bytes_of = reinterpret_cast<unsigned int*>(dst_of + stages);
-
-    // Let the next migration grid of the stream start while this one is still running (its ramp-up
-    // then hides this grid's tail).  The host sets wait_prior when the two grids are not independent.
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    for (unsigned int s = 0; s < stages; ++s) mbar_init(&bars[s], 1);
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    fence_async_proxy();
-    if (p.wait_prior) asm volatile("griddepcontrol.wait;" ::: "memory");
-
-    const unsigned long long pol = l2_evict_first_policy();
-
-    // Work distribution.  With a counter pair (work[0] next unit, work[1] finished CTAs) CTAs draw batches of
-    // consecutive units on demand, so no CTA is left finishing a fixed share after the others are done; without
-    // one, units are dealt round-robin (unit = blockIdx.x + k * gridDim.x).
-    int* const work = p.work;
-    const unsigned int batch = p.batch ? p.batch : 1u;
-    unsigned int batch_next = 0, batch_end = 0, fetched = 0;
-    bool exhausted = false;
-    auto next_unit = [&]() -> unsigned int {
-        if (work) {
-            if (batch_next == batch_end) {
-                batch_next = (unsigned int)atomicAdd(work, (int)batch);
-                batch_end = batch_next + batch;
-            }
-            return batch_next++;
-        }
-        return blockIdx.x + (fetched++) * gridDim.x;
-    };
-
-    unsigned int issued = 0;
-    auto try_issue = [&]() {
-        const unsigned int u = next_unit();
-        if (u >= p.total_units) {
-            exhausted = true;
-            return;
-        }
-        const unsigned int s = issued % stages;
-        Unit w = decode_unit(p, src_ids, dst_ids, u);
-        dst_of[s] = w.dst;
-        bytes_of[s] = w.bytes;
-        mbar_expect_tx(&bars[s], w.bytes);
-        if (p.lose_unit_plus1 && u + 1u == p.lose_unit_plus1) {
-            // Failure-path exercise: the barrier is armed but the load is never issued, so the wait below
-            // must run out and report.  Nothing is in flight towards this stage, so leaving is safe.
-        } else if (p.l2_hint & 1u) {
-            bulk_g2s_hint(ring + (size_t)s * stage_bytes, w.src, w.bytes, &bars[s], pol);
-        } else {
-            bulk_g2s(ring + (size_t)s * stage_bytes, w.src, w.bytes, &bars[s]);
-        }
-        ++issued;
-    };
-
-    for (unsigned int i = 0; i < stages && !exhausted; ++i) try_issue();
-
-    unsigned int waited = 0;   // loads whose barrier has been observed complete
-    bool ok = true;
-    for (unsigned int k = 0; k < issued; ++k) {      // `issued` grows while units remain
-        const unsigned int s = k % stages;
-        if (!mbar_wait_bounded(&bars[s], (k / stages) & 1u, p.wait_limit_ns)) {
-            p.status[0] = kDevLoadTimeout;
-            p.status[1] = (int)k;
-            ok = false;
-            break;
-        }
-        waited = k + 1;
-        if (p.l2_hint & 2u) bulk_s2g_hint(dst_of[s], ring + (size_t)s * stage_bytes, bytes_of[s], pol);
-        else bulk_s2g(dst_of[s], ring + (size_t)s * stage_bytes, bytes_of[s]);
-        bulk_commit();
-        // Refill the stage whose store was issued one iteration ago: by now only the
-        // newest store group may still be reading shared memory.
-        if (k >= 1 && !exhausted) {
-            bulk_wait_read<1>();
-            try_issue();
-        }
-    }
-    if (!ok) {
-        // Give every load already in flight a bounded chance to land before the
-        // shared memory it targets is released.
-        for (unsigned int k = waited + 1; k < issued; ++k)
-            if (!mbar_wait_bounded(&bars[k % stages], (k / stages) & 1u, p.wait_limit_ns)) { p.status[2] = kDevDrainTimeout; break; }
-    }
-    bulk_wait_all();
-    // A grid that was allowed to start before its predecessor finished must not *finish* before it: whatever
-    // follows in the stream waits only for this grid, and must thereby have waited for every earlier one.
-    if (!p.wait_prior) asm volatile("griddepcontrol.wait;" ::: "memory");
-    if (work) {
-        // The last CTA to finish rearms the counter pair for the next launch that uses it.
-        __threadfence();
-        if (atomicAdd(work + 1, 1) == (int)gridDim.x - 1) {
-            work[0] = 0;
-            work[1] = 0;
-            __threadfence();
-        }
-    }
-}
-
-// Block tables in device memory (any number of blocks).
-__global__ void __launch_bounds__(32) kv_migrate_bulk(const __grid_constant__ MigParams p,
-                                                       unsigned int stages, unsigned int stage_bytes) {
-    bulk_pipeline(p, p.src_ids, p.dst_ids, stages, stage_bytes);
-}
-
-// Block tables carried in the kernel's own parameter block ([src ids | dst ids], n_blocks each):
-// a typical request (<= 256 blocks) then needs no table upload ahead of the launch, which removes a
-// copy-engine hop from the latency of every call.
-template <int NIDS>
-struct MigParamsInline {
-    MigParams base;
-    int ids[2 * NIDS];
-};
-
-template <int NIDS>
-__global__ void __launch_bounds__(32) kv_migrate_bulk_inline(const __grid_constant__ MigParamsInline<NIDS> q,
-                                                              unsigned int stages, unsigned int stage_bytes) {
-    bulk_pipeline(q.base, q.ids, q.ids + q.base.n_blocks, stages, stage_bytes);
-}
 
 // ---------------------------------------------------------------------------
 // Host side
@@ -615,47 +321,11 @@ int pick_vec(uintptr_t bits) {
 constexpr int kInlineSmall = 256;    // block ids per table that fit the classic 4 KB parameter block
 constexpr int kInlineLarge = 1024;   // needs the large (32 KB) parameter block of recent drivers
 
-template <int NIDS>
-cudaError_t launch_bulk_inline(const MigParams& p, const int64_t* src, const int64_t* dst, unsigned grid, size_t smem,
-                               cudaStream_t stream, int64_t stages, int64_t chunk, bool overlap) {
-    static_assert(sizeof(MigParamsInline<kInlineSmall>) <= 4096, "small inline tables must fit 4 KB of parameters");
-    MigParamsInline<NIDS> q;
-    q.base = p;
-    q.base.src_ids = q.base.dst_ids = nullptr;
-    const unsigned n = p.n_blocks;
-    for (unsigned i = 0; i < n; ++i) {
-        q.ids[i] = (int)src[i];
-        q.ids[n + i] = (int)dst[i];
-    }
-    // Programmatic stream serialization: this grid may begin once the previous grid of the stream has
-    // executed griddepcontrol.launch_dependents (our own kernels do so at once; any other kernel
-    // triggers only by finishing, which leaves ordinary stream order in place).
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(grid);
-    cfg.blockDim = dim3(32);
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = overlap ? 1 : 0;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, kv_migrate_bulk_inline<NIDS>, q, (unsigned)stages, (unsigned)chunk);
-}
+// ---- pieces shared by every migration entry point ---------------------------------------------
 
-template <int VEC>
-cudaError_t launch_vec(const MigParams& p, unsigned grid, cudaStream_t stream) {
-    kv_migrate_vec<VEC><<<grid, kVecThreads, 0, stream>>>(p);
-    return cudaGetLastError();
-}
-
-int enqueue_migration(int64_t ctx_pp, int64_t ctx_tp, const int64_t* ctx_blocks, int64_t n_ctx, int64_t dec_pp,
-                      int64_t dec_tp, int64_t dec_pp_rank, int64_t dec_tp_rank, const int64_t* dec_blocks, int64_t n_dec,
-                      void* k_cache, void* v_cache, const kvmig_pool_shape* shape, cudaStream_t stream, uint64_t* ticket,
-                      int64_t layer_begin = 0, int64_t layer_end = INT64_MAX) {
-    g_err.clear();
-    if (ticket) *ticket = 0;
-    int rc = check_shape(shape, "migrate_blocks");
+int check_lists(const char* what, const kvmig_pool_shape* shape, const int64_t* ctx_blocks, int64_t n_ctx,
+                const int64_t* dec_blocks, int64_t n_dec, const void* k_cache, const void* v_cache) {
+    int rc = check_shape(shape, what);
     if (rc) return rc;
     if (n_ctx < 0 || n_dec < 0) return fail(KVMIG_EINVAL, "negative list length");
     if (n_ctx != n_dec)
@@ -663,44 +333,38 @@ int enqueue_migration(int64_t ctx_pp, int64_t ctx_tp, const int64_t* ctx_blocks,
                     (long long)n_ctx, (long long)n_dec);
     if (n_ctx > 0 && (!ctx_blocks || !dec_blocks)) return fail(KVMIG_EINVAL, "block index list is NULL");
     if (!k_cache || !v_cache) return fail(KVMIG_EINVAL, "k_cache / v_cache is NULL");
+    return 0;
+}
 
-    std::lock_guard<std::mutex> lock(g_mu);
-    DeviceState* stp;
-    int dev;
-    rc = ensure_device(&stp, &dev);
-    if (rc) return rc;
-    DeviceState& st = *stp;
-
-    const int64_t L = shape->num_layers * dec_pp, H = shape->num_heads * dec_tp;
-    std::vector<SegPlan> plan;
-    rc = plan_segments(L, H, ctx_tp, ctx_pp, dec_tp, dec_tp_rank, dec_pp, dec_pp_rank, &plan);
-    if (rc) return rc;
-    // Optional window of global layers: keep only the part of each segment that lies inside it.
-    if (layer_begin < 0 || layer_end < layer_begin)
-        return fail(KVMIG_EINVAL, "layer window [%lld, %lld) is not a range", (long long)layer_begin, (long long)layer_end);
-    layer_end = std::min(layer_end, L);
-    const bool windowed = layer_begin > 0 || layer_end < L;
-    if (windowed) {
-        const int64_t first_layer = dec_pp_rank * shape->num_layers;   // global index of this worker's local layer 0
-        std::vector<SegPlan> clipped;
-        for (SegPlan sp : plan) {
-            const int64_t g0 = first_layer + sp.dst_layer_off, g1 = g0 + sp.n_layers;
-            const int64_t a = std::max(g0, layer_begin), b = std::min(g1, layer_end);
-            if (a >= b) continue;
-            sp.src_layer_off += a - g0;
-            sp.dst_layer_off += a - g0;
-            sp.n_layers = b - a;
-            clipped.push_back(sp);
-        }
-        plan.swap(clipped);
+// Keep only the part of each planned overlap that lies inside the window of global layers.
+void clip_to_layers(std::vector<SegPlan>* plan, int64_t first_layer, int64_t layer_begin, int64_t layer_end) {
+    std::vector<SegPlan> clipped;
+    for (SegPlan sp : *plan) {
+        const int64_t g0 = first_layer + sp.dst_layer_off, g1 = g0 + sp.n_layers;
+        const int64_t a = std::max(g0, layer_begin), b = std::min(g1, layer_end);
+        if (a >= b) continue;
+        sp.src_layer_off += a - g0;
+        sp.dst_layer_off += a - g0;
+        sp.n_layers = b - a;
+        clipped.push_back(sp);
     }
+    plan->swap(clipped);
+}
 
+struct Assembly {
+    std::vector<Seg> segs;             // two per contributing context worker: K pool, V pool
+    uintptr_t align_bits = 0;          // OR of every address, stride and run length
+    int64_t src_num_blocks = INT64_MAX;
+};
+
+// Turn the planned overlaps into strided-copy descriptors over the registered (mapped) context pools.
+// With map_missing a registered-but-unmapped pool is mapped now; without, that is an error (mapping
+// reserves address space, which the allocation-free entry point must not do).
+int assemble_segments(DeviceState& st, int dev, const std::vector<SegPlan>& plan, int64_t L, int64_t H, int64_t ctx_tp,
+                      int64_t ctx_pp, const kvmig_pool_shape* shape, void* k_cache, void* v_cache, bool map_missing,
+                      Assembly* out) {
     const int64_t slab = shape->block_size * shape->head_dim * shape->elem_size;
     const int64_t Lc = L / ctx_pp, Hc = H / ctx_tp;
-    int64_t src_num_blocks = INT64_MAX;
-    std::vector<Seg> segs;
-    uintptr_t align_bits = 0;
-    int64_t chunk = g_opt.chunk_bytes.load();
     for (const SegPlan& sp : plan) {
         auto it = st.registry.find(sp.ctx);
         if (it == st.registry.end())
@@ -717,13 +381,18 @@ int enqueue_migration(int64_t ctx_pp, int64_t ctx_tp, const int64_t* ctx_blocks,
             return fail(KVMIG_EINVAL, "context pool block geometry (%lld x %lld x %lld B) differs from the decoding pool's",
                         (long long)ss.block_size, (long long)ss.head_dim, (long long)ss.elem_size);
         if (!ce.mapped) {
-            rc = map_pool(st, dev, ce.hk.data(), &ce.k);
+            if (!map_missing)
+                return fail(KVMIG_ENOTREG,
+                            "context worker (pp_rank %lld, tp_rank %lld) was registered for another decoding rank and is not "
+                            "mapped; register it with this worker's parallel config first",
+                            (long long)sp.ctx.pp_rank, (long long)sp.ctx.tp_rank);
+            int rc = map_pool(st, dev, ce.hk.data(), &ce.k);
             if (rc) return rc;
             rc = map_pool(st, dev, ce.hv.data(), &ce.v);
             if (rc) return rc;
             ce.mapped = true;
         }
-        src_num_blocks = std::min(src_num_blocks, std::min(ce.hk[HW_NB], ce.hv[HW_NB]));
+        out->src_num_blocks = std::min(out->src_num_blocks, std::min(ce.hk[HW_NB], ce.hv[HW_NB]));
         for (int x = 0; x < 2; ++x) {
             Seg g;
             const char* sbase = x == 0 ? ce.k : ce.v;
@@ -740,65 +409,197 @@ int enqueue_migration(int64_t ctx_pp, int64_t ctx_tp, const int64_t* ctx_blocks,
                 g.run_bytes *= g.rows;   // whole layers on both sides: rows are adjacent
                 g.rows = 1;
             }
-            align_bits |= (uintptr_t)g.src | (uintptr_t)g.dst | g.src_block_stride | g.dst_block_stride |
-                          g.src_row_stride | g.dst_row_stride | g.run_bytes;
-            segs.push_back(g);
+            out->align_bits |= (uintptr_t)g.src | (uintptr_t)g.dst | g.src_block_stride | g.dst_block_stride |
+                               g.src_row_stride | g.dst_row_stride | g.run_bytes;
+            out->segs.push_back(g);
         }
     }
+    return 0;
+}
 
-    // Validate ids before anything is enqueued.  `seen` is a per-device bitmap kept all-zero between calls.
+// Ids in range on both sides, no target named twice.  `st.seen` is a bitmap kept all-zero between calls.
+int validate_ids(DeviceState& st, const int64_t* ctx_blocks, const int64_t* dec_blocks, int64_t n, int64_t src_num_blocks,
+                 int64_t dst_num_blocks) {
     std::vector<char>& seen = st.seen;
-    if ((int64_t)seen.size() < shape->num_blocks) seen.resize((size_t)shape->num_blocks, 0);
+    if ((int64_t)seen.size() < dst_num_blocks) seen.resize((size_t)dst_num_blocks, 0);
     int64_t checked = 0;
-    rc = 0;
-    for (; checked < n_ctx && !rc; ++checked) {
+    int rc = 0;
+    for (; checked < n && !rc; ++checked) {
         const int64_t i = checked;
         if (ctx_blocks[i] < 0 || ctx_blocks[i] >= src_num_blocks)
             rc = fail(KVMIG_EINVAL, "context_block_indexes[%lld] = %lld is outside the context pool (%lld blocks)", (long long)i,
                       (long long)ctx_blocks[i], (long long)src_num_blocks);
-        else if (dec_blocks[i] < 0 || dec_blocks[i] >= shape->num_blocks)
+        else if (dec_blocks[i] < 0 || dec_blocks[i] >= dst_num_blocks)
             rc = fail(KVMIG_EINVAL, "decoding_block_indexes[%lld] = %lld is outside the decoding pool (%lld blocks)",
-                      (long long)i, (long long)dec_blocks[i], (long long)shape->num_blocks);
+                      (long long)i, (long long)dec_blocks[i], (long long)dst_num_blocks);
         else if (seen[(size_t)dec_blocks[i]])
             rc = fail(KVMIG_EINVAL, "decoding_block_indexes names block %lld twice", (long long)dec_blocks[i]);
         else
             seen[(size_t)dec_blocks[i]] = 1;
     }
     for (int64_t i = 0; i < checked; ++i)
-        if (dec_blocks[i] >= 0 && dec_blocks[i] < shape->num_blocks) seen[(size_t)dec_blocks[i]] = 0;
+        if (dec_blocks[i] >= 0 && dec_blocks[i] < dst_num_blocks) seen[(size_t)dec_blocks[i]] = 0;
+    return rc;
+}
+
+struct LaunchShape {
+    int64_t kernel = 0;        // 1 vector loads, 2 bulk-copy pipeline
+    int vec = 16;              // widest vector every address and length allows
+    int64_t stages = 0, chunk = 0, ctas_per_sm = 0;
+    size_t smem = 0;
+};
+
+// Kernel, ring geometry and CTAs per SM from the options and the alignment of this call.
+int shape_launch(DeviceState& st, uintptr_t align_bits, LaunchShape* ls) {
+    ls->vec = pick_vec(align_bits);
+    ls->kernel = g_opt.kernel.load();
+    if (ls->kernel == 0) ls->kernel = (ls->vec == 16) ? 2 : 1;
+    if (ls->kernel == 2 && ls->vec != 16)
+        return fail(KVMIG_EINVAL, "the bulk-copy kernel needs 16-byte aligned runs; this shape gives %d", ls->vec);
+    ls->stages = std::min<int64_t>(std::max<int64_t>(g_opt.stages.load(), 2), kMaxStages);
+    ls->chunk = g_opt.chunk_bytes.load();
+    if (ls->chunk < 16 || ls->chunk % 16) return fail(KVMIG_EINVAL, "chunk_bytes must be a positive multiple of 16");
+    ls->ctas_per_sm = g_opt.ctas_per_sm.load();
+    if (ls->kernel == 2) {
+        ls->smem = (size_t)ls->stages * ls->chunk + (size_t)ls->stages * (8 + 8 + 4) + 16;
+        if ((int64_t)ls->smem > st.max_smem_optin)
+            return fail(KVMIG_ELIMIT, "stages x chunk_bytes = %zu B exceeds the %d B of shared memory a CTA may use", ls->smem,
+                        st.max_smem_optin);
+        if (ls->ctas_per_sm <= 0) {
+            const int64_t ring = ls->stages * ls->chunk, target = 96 * 1024;   // bytes in flight per SM
+            ls->ctas_per_sm = std::max<int64_t>(1, std::min<int64_t>(8, (target + ring - 1) / ring));
+            ls->ctas_per_sm = std::min<int64_t>(ls->ctas_per_sm, std::max<int64_t>(1, (220 * 1024) / (int64_t)(ls->smem + 1024)));
+        }
+        if ((int)ls->smem > st.bulk_smem_set) {
+            const int bytes = (int)ls->smem;
+            CU_TRY(cudaFuncSetAttribute(kv_migrate_bulk, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+            CU_TRY(cudaFuncSetAttribute(kv_migrate_bulk_inline<kInlineSmall>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+            CU_TRY(cudaFuncSetAttribute(kv_migrate_bulk_inline<kInlineLarge>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+            st.bulk_smem_set = bytes;
+        }
+    } else if (ls->ctas_per_sm <= 0) {
+        ls->ctas_per_sm = 8;
+    }
+    return 0;
+}
+
+// Fill the descriptors of one launch (at most kMaxSegs segments); returns the work units per block.
+unsigned fill_launch(MigParams* p, const Seg* segs, unsigned nseg, const LaunchShape& ls, int* status, int64_t* bytes_per_block) {
+    std::memset(p, 0, sizeof *p);
+    p->nseg = nseg;
+    unsigned upb = 0;
+    for (unsigned s = 0; s < nseg; ++s) {
+        Seg g = segs[s];
+        g.chunks_per_run = (unsigned)((g.run_bytes + ls.chunk - 1) / ls.chunk);
+        g.units_per_block = g.rows * g.chunks_per_run;
+        g.unit_begin = upb;
+        upb += g.units_per_block;
+        p->seg[s] = g;
+        *bytes_per_block += (int64_t)g.run_bytes * g.rows;
+    }
+    p->status = status;
+    p->units_per_block = upb;
+    p->chunk_bytes = (unsigned)ls.chunk;
+    p->batch = 1;
+    p->l2_hint = (unsigned)g_opt.l2_hint.load();
+    p->wait_limit_ns = (unsigned long long)std::max<int64_t>(1, g_opt.wait_limit_ms.load()) * 1000000ULL;
+    p->lose_unit_plus1 = (unsigned)g_opt.lose_unit_plus1.load();
+    return upb;
+}
+
+unsigned grid_for(const DeviceState& st, const LaunchShape& ls, unsigned total_units) {
+    unsigned grid = (unsigned)std::min<int64_t>(total_units, (int64_t)st.sm_count * ls.ctas_per_sm);
+    // A cap on the grid leaves whole SMs to a decode step running beside the migration.
+    if (const int64_t cap = g_opt.max_ctas.load(); cap > 0) grid = (unsigned)std::min<int64_t>(grid, cap);
+    return grid;
+}
+
+template <int NIDS>
+cudaError_t launch_bulk_inline(const MigParams& p, const int64_t* src, const int64_t* dst, unsigned grid, const LaunchShape& ls,
+                               cudaStream_t stream, bool overlap) {
+    static_assert(sizeof(MigParamsInline<kInlineSmall>) <= 4096, "small inline tables must fit 4 KB of parameters");
+    MigParamsInline<NIDS> q;
+    q.base = p;
+    q.base.src_ids = q.base.dst_ids = nullptr;
+    const unsigned n = p.n_blocks;
+    for (unsigned i = 0; i < n; ++i) {
+        q.ids[i] = (int)src[i];
+        q.ids[n + i] = (int)dst[i];
+    }
+    // Programmatic stream serialization: this grid may begin once the previous grid of the stream has
+    // executed griddepcontrol.launch_dependents (our own kernels do so at once; any other kernel
+    // triggers only by finishing, which leaves ordinary stream order in place).
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(32);
+    cfg.dynamicSmemBytes = ls.smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = overlap ? 1 : 0;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kv_migrate_bulk_inline<NIDS>, q, (unsigned)ls.stages, (unsigned)ls.chunk);
+}
+
+template <int VEC>
+cudaError_t launch_vec(const MigParams& p, unsigned grid, cudaStream_t stream) {
+    kv_migrate_vec<VEC><<<grid, kVecThreads, 0, stream>>>(p);
+    return cudaGetLastError();
+}
+
+// Launch with the block tables in device memory (p.src_ids / p.dst_ids), ordinary stream order.
+cudaError_t launch_device_tables(const MigParams& p, unsigned grid, const LaunchShape& ls, cudaStream_t stream) {
+    if (ls.kernel == 2) {
+        kv_migrate_bulk<<<grid, 32, ls.smem, stream>>>(p, (unsigned)ls.stages, (unsigned)ls.chunk);
+        return cudaGetLastError();
+    }
+    switch (ls.vec) {
+        case 16: return launch_vec<16>(p, grid, stream);
+        case 8: return launch_vec<8>(p, grid, stream);
+        case 4: return launch_vec<4>(p, grid, stream);
+        case 2: return launch_vec<2>(p, grid, stream);
+        default: return launch_vec<1>(p, grid, stream);
+    }
+}
+
+// ---- the ticketed entry point (awaited and asynchronous calls, optional layer window) ----------
+
+int enqueue_migration(int64_t ctx_pp, int64_t ctx_tp, const int64_t* ctx_blocks, int64_t n_ctx, int64_t dec_pp,
+                      int64_t dec_tp, int64_t dec_pp_rank, int64_t dec_tp_rank, const int64_t* dec_blocks, int64_t n_dec,
+                      void* k_cache, void* v_cache, const kvmig_pool_shape* shape, cudaStream_t stream, uint64_t* ticket,
+                      int64_t layer_begin = 0, int64_t layer_end = INT64_MAX) {
+    g_err.clear();
+    if (ticket) *ticket = 0;
+    int rc = check_lists("migrate_blocks", shape, ctx_blocks, n_ctx, dec_blocks, n_dec, k_cache, v_cache);
+    if (rc) return rc;
+
+    std::lock_guard<std::mutex> lock(g_mu);
+    DeviceState* stp;
+    int dev;
+    rc = ensure_device(&stp, &dev);
+    if (rc) return rc;
+    DeviceState& st = *stp;
+
+    const int64_t L = shape->num_layers * dec_pp, H = shape->num_heads * dec_tp;
+    std::vector<SegPlan> plan;
+    rc = plan_segments(L, H, ctx_tp, ctx_pp, dec_tp, dec_tp_rank, dec_pp, dec_pp_rank, &plan);
+    if (rc) return rc;
+    if (layer_begin < 0 || layer_end < layer_begin)
+        return fail(KVMIG_EINVAL, "layer window [%lld, %lld) is not a range", (long long)layer_begin, (long long)layer_end);
+    layer_end = std::min(layer_end, L);
+    if (layer_begin > 0 || layer_end < L) clip_to_layers(&plan, dec_pp_rank * shape->num_layers, layer_begin, layer_end);
+
+    Assembly as;
+    rc = assemble_segments(st, dev, plan, L, H, ctx_tp, ctx_pp, shape, k_cache, v_cache, /*map_missing=*/true, &as);
+    if (rc) return rc;
+    rc = validate_ids(st, ctx_blocks, dec_blocks, n_ctx, as.src_num_blocks, shape->num_blocks);
     if (rc) return rc;
     if (n_ctx == 0 || plan.empty()) return 0;   // nothing to move (empty lists, or the window misses this worker)
 
-    // Kernel choice.
-    const int vec = pick_vec(align_bits);
-    int64_t kernel = g_opt.kernel.load();
-    if (kernel == 0) kernel = (vec == 16) ? 2 : 1;
-    if (kernel == 2 && vec != 16) return fail(KVMIG_EINVAL, "the bulk-copy kernel needs 16-byte aligned runs; this shape gives %d", vec);
-    int64_t stages = std::min<int64_t>(std::max<int64_t>(g_opt.stages.load(), 2), kMaxStages);
-    if (chunk < 16 || chunk % 16) return fail(KVMIG_EINVAL, "chunk_bytes must be a positive multiple of 16");
-    size_t smem = 0;
-    int64_t ctas_per_sm = g_opt.ctas_per_sm.load();
-    if (kernel == 2) {
-        smem = (size_t)stages * chunk + (size_t)stages * (8 + 8 + 4) + 16;
-        if ((int64_t)smem > st.max_smem_optin)
-            return fail(KVMIG_ELIMIT, "stages x chunk_bytes = %zu B exceeds the %d B of shared memory a CTA may use", smem,
-                        st.max_smem_optin);
-        if (ctas_per_sm <= 0) {
-            const int64_t ring = stages * chunk, target = 96 * 1024;   // bytes in flight per SM
-            ctas_per_sm = std::max<int64_t>(1, std::min<int64_t>(8, (target + ring - 1) / ring));
-            ctas_per_sm = std::min<int64_t>(ctas_per_sm, std::max<int64_t>(1, (220 * 1024) / (int64_t)(smem + 1024)));
-        }
-        if ((int)smem > st.bulk_smem_set) {
-            CU_TRY(cudaFuncSetAttribute(kv_migrate_bulk, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            CU_TRY(cudaFuncSetAttribute(kv_migrate_bulk_inline<kInlineSmall>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                        (int)smem));
-            CU_TRY(cudaFuncSetAttribute(kv_migrate_bulk_inline<kInlineLarge>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                        (int)smem));
-            st.bulk_smem_set = (int)smem;
-        }
-    } else if (ctas_per_sm <= 0) {
-        ctas_per_sm = 8;
-    }
+    LaunchShape ls;
+    rc = shape_launch(st, as.align_bits, &ls);
+    if (rc) return rc;
 
     // Ticket slot.
     uint64_t seq = st.next_seq++;
@@ -806,7 +607,7 @@ int enqueue_migration(int64_t ctx_pp, int64_t ctx_tp, const int64_t* ctx_blocks,
     rc = retire_slot(st, sl);
     if (rc && !st.sticky_error) { st.sticky_error = rc; st.sticky_text = g_err; }
     // Tables of a typical request ride in the kernel parameters; longer lists go through device memory.
-    const bool inline_tables = kernel == 2 && g_opt.inline_tables.load() != 0 && n_ctx <= kInlineLarge;
+    const bool inline_tables = ls.kernel == 2 && g_opt.inline_tables.load() != 0 && n_ctx <= kInlineLarge;
     rc = grow_slot(sl, inline_tables ? 0 : n_ctx);
     if (rc) return rc;
     sl.status[0] = sl.status[1] = sl.status[2] = sl.status[3] = 0;
@@ -843,69 +644,36 @@ int enqueue_migration(int64_t ctx_pp, int64_t ctx_tp, const int64_t* ctx_blocks,
 
     int64_t bytes_per_block = 0;
     int launch_index = 0;
-    for (size_t s0 = 0; s0 < segs.size(); s0 += kMaxSegs) {
+    for (size_t s0 = 0; s0 < as.segs.size(); s0 += kMaxSegs) {
         MigParams p;
-        std::memset(&p, 0, sizeof p);
-        p.nseg = (unsigned)std::min<size_t>(kMaxSegs, segs.size() - s0);
-        unsigned upb = 0;
-        for (unsigned s = 0; s < p.nseg; ++s) {
-            Seg g = segs[s0 + s];
-            g.chunks_per_run = (unsigned)((g.run_bytes + chunk - 1) / chunk);
-            g.units_per_block = g.rows * g.chunks_per_run;
-            g.unit_begin = upb;
-            upb += g.units_per_block;
-            p.seg[s] = g;
-            bytes_per_block += (int64_t)g.run_bytes * g.rows;
-        }
-        p.src_ids = sl.d_tab;
-        p.dst_ids = sl.d_tab + n_ctx;
-        p.status = sl.status_dev;
-        p.n_blocks = (unsigned)n_ctx;
-        p.units_per_block = upb;
-        p.chunk_bytes = (unsigned)chunk;
+        const unsigned nseg = (unsigned)std::min<size_t>(kMaxSegs, as.segs.size() - s0);
+        const unsigned upb = fill_launch(&p, as.segs.data() + s0, nseg, ls, sl.status_dev, &bytes_per_block);
         p.wait_prior = depends ? 1u : 0u;
-        p.l2_hint = (unsigned)g_opt.l2_hint.load();
-        p.wait_limit_ns = (unsigned long long)std::max<int64_t>(1, g_opt.wait_limit_ms.load()) * 1000000ULL;
-        p.lose_unit_plus1 = (unsigned)g_opt.lose_unit_plus1.load();
         // total_units is 32-bit: walk the block list in slices if a launch would overflow.
         const int64_t max_blocks = std::max<int64_t>(1, (int64_t)0x7fffffff / upb);
         for (int64_t b0 = 0; b0 < n_ctx; b0 += max_blocks) {
-            int64_t nb = std::min(max_blocks, n_ctx - b0);
-            p.src_ids = sl.d_tab + b0;
-            p.dst_ids = sl.d_tab + n_ctx + b0;
+            const int64_t nb = std::min(max_blocks, n_ctx - b0);
+            p.src_ids = inline_tables ? nullptr : sl.d_tab + b0;
+            p.dst_ids = inline_tables ? nullptr : sl.d_tab + n_ctx + b0;
             p.n_blocks = (unsigned)nb;
             p.total_units = (unsigned)(nb * upb);
-            unsigned grid = (unsigned)std::min<int64_t>(p.total_units, (int64_t)st.sm_count * ctas_per_sm);
-            // A cap on the grid leaves whole SMs to a decode step running beside the migration.
-            if (const int64_t cap = g_opt.max_ctas.load(); cap > 0) grid = (unsigned)std::min<int64_t>(grid, cap);
-            // Each launch of this call gets its own counter pair (launches of one call may overlap).
+            const unsigned grid = grid_for(st, ls, p.total_units);
+            // Each launch of this call gets its own counter pair (launches of one call may overlap).  A short
+            // launch keeps the fixed deal: the counter's latency would be most of its run time.
             p.work = nullptr;
             p.batch = 1;
-            // (A short launch keeps the fixed deal: the counter's latency would be most of its run time.)
-            if (kernel == 2 && g_opt.dynamic_units.load() != 0 && launch_index < kWorkPairs && p.total_units >= 4u * grid) {
+            if (ls.kernel == 2 && g_opt.dynamic_units.load() != 0 && launch_index < kWorkPairs && p.total_units >= 4u * grid) {
                 p.work = sl.work + 2 * launch_index;
                 p.batch = p.total_units >= 32u * grid ? 4u : (p.total_units >= 8u * grid ? 2u : 1u);
             }
             ++launch_index;
             cudaError_t e;
-            if (inline_tables) {
-                e = n_ctx <= kInlineSmall
-                        ? launch_bulk_inline<kInlineSmall>(p, ctx_blocks + b0, dec_blocks + b0, grid, smem, stream, stages, chunk,
-                                                           overlap)
-                        : launch_bulk_inline<kInlineLarge>(p, ctx_blocks + b0, dec_blocks + b0, grid, smem, stream, stages,
-                                                           chunk, overlap);
-            } else if (kernel == 2) {
-                kv_migrate_bulk<<<grid, 32, smem, stream>>>(p, (unsigned)stages, (unsigned)chunk);
-                e = cudaGetLastError();
-            } else {
-                switch (vec) {
-                    case 16: e = launch_vec<16>(p, grid, stream); break;
-                    case 8: e = launch_vec<8>(p, grid, stream); break;
-                    case 4: e = launch_vec<4>(p, grid, stream); break;
-                    case 2: e = launch_vec<2>(p, grid, stream); break;
-                    default: e = launch_vec<1>(p, grid, stream); break;
-                }
-            }
+            if (inline_tables)
+                e = nb <= kInlineSmall
+                        ? launch_bulk_inline<kInlineSmall>(p, ctx_blocks + b0, dec_blocks + b0, grid, ls, stream, overlap)
+                        : launch_bulk_inline<kInlineLarge>(p, ctx_blocks + b0, dec_blocks + b0, grid, ls, stream, overlap);
+            else
+                e = launch_device_tables(p, grid, ls, stream);
             if (e != cudaSuccess) return fail(KVMIG_ECUDA, "launching the migration kernel: %s", cudaGetErrorString(e));
             g_cnt.kernel_launches++;
         }
@@ -991,19 +759,13 @@ int migrate_static(int64_t ctx_pp, int64_t ctx_tp, const int64_t* ctx_blocks, in
                    int64_t dec_pp_rank, int64_t dec_tp_rank, const int64_t* dec_blocks, int64_t n_dec, void* k_cache,
                    void* v_cache, const kvmig_pool_shape* shape, cudaStream_t stream) {
     g_err.clear();
-    int rc = check_shape(shape, "migrate_blocks_static");
+    int rc = check_lists("migrate_blocks_static", shape, ctx_blocks, n_ctx, dec_blocks, n_dec, k_cache, v_cache);
     if (rc) return rc;
-    if (n_ctx < 0 || n_dec < 0) return fail(KVMIG_EINVAL, "negative list length");
-    if (n_ctx != n_dec)
-        return fail(KVMIG_EINVAL, "context_block_indexes has %lld entries but decoding_block_indexes has %lld",
-                    (long long)n_ctx, (long long)n_dec);
     if (n_ctx > KVMIG_STATIC_MAX_BLOCKS)
         return fail(KVMIG_ELIMIT,
                     "%lld blocks in one call exceed the %d the built-in scratch holds; split the lists or use "
                     "kvmig_migrate_blocks",
                     (long long)n_ctx, KVMIG_STATIC_MAX_BLOCKS);
-    if (n_ctx > 0 && (!ctx_blocks || !dec_blocks)) return fail(KVMIG_EINVAL, "block index list is NULL");
-    if (!k_cache || !v_cache) return fail(KVMIG_EINVAL, "k_cache / v_cache is NULL");
 
     std::lock_guard<std::mutex> lock(g_mu);
     DeviceState* stp;
@@ -1022,90 +784,20 @@ int migrate_static(int64_t ctx_pp, int64_t ctx_tp, const int64_t* ctx_blocks, in
     if (plan.size() * 2 > (size_t)kMaxSegs)
         return fail(KVMIG_ELIMIT, "this reshard needs %zu segments; the allocation-free entry point takes %d", plan.size() * 2,
                     kMaxSegs);
-    const int64_t slab = shape->block_size * shape->head_dim * shape->elem_size;
-    const int64_t Lc = L / ctx_pp, Hc = H / ctx_tp;
-    const int64_t chunk = g_opt.chunk_bytes.load();
-    MigParams p;
-    std::memset(&p, 0, sizeof p);
-    int64_t src_num_blocks = INT64_MAX, bytes_per_block = 0;
-    uintptr_t align_bits = 0;
-    unsigned upb = 0;
-    for (const SegPlan& sp : plan) {
-        auto it = st.registry.find(sp.ctx);
-        if (it == st.registry.end())
-            return fail(KVMIG_ENOTREG, "context worker (pp_rank %lld, tp_rank %lld) is not registered on this device",
-                        (long long)sp.ctx.pp_rank, (long long)sp.ctx.tp_rank);
-        const CtxEntry& ce = it->second;
-        if (!ce.mapped)   // mapping a peer pool reserves address space; that belongs to registration, not to this call
-            return fail(KVMIG_ENOTREG,
-                        "context worker (pp_rank %lld, tp_rank %lld) was registered for another decoding rank and is not "
-                        "mapped; register it with this worker's parallel config first",
-                        (long long)sp.ctx.pp_rank, (long long)sp.ctx.tp_rank);
-        if (ce.L != L || ce.H != H) return fail(KVMIG_EINVAL, "registered model shape differs from this worker's");
-        kvmig_pool_shape ss = shape_of_handle(ce.hk.data());
-        if (ss.block_size != shape->block_size || ss.head_dim != shape->head_dim || ss.elem_size != shape->elem_size)
-            return fail(KVMIG_EINVAL, "context pool block geometry differs from the decoding pool's");
-        src_num_blocks = std::min(src_num_blocks, std::min(ce.hk[HW_NB], ce.hv[HW_NB]));
-        for (int x = 0; x < 2; ++x) {
-            Seg g;
-            g.src_block_stride = Lc * Hc * slab;
-            g.dst_block_stride = shape->num_layers * shape->num_heads * slab;
-            g.src_row_stride = Hc * slab;
-            g.dst_row_stride = shape->num_heads * slab;
-            g.run_bytes = sp.n_heads * slab;
-            g.rows = (unsigned)sp.n_layers;
-            g.src = (x == 0 ? ce.k : ce.v) + sp.src_layer_off * g.src_row_stride + sp.src_head_off * slab;
-            g.dst = static_cast<char*>(x == 0 ? k_cache : v_cache) + sp.dst_layer_off * g.dst_row_stride + sp.dst_head_off * slab;
-            if (g.run_bytes == g.src_row_stride && g.run_bytes == g.dst_row_stride) {
-                g.run_bytes *= g.rows;
-                g.rows = 1;
-            }
-            align_bits |= (uintptr_t)g.src | (uintptr_t)g.dst | g.src_block_stride | g.dst_block_stride | g.src_row_stride |
-                          g.dst_row_stride | g.run_bytes;
-            g.chunks_per_run = (unsigned)((g.run_bytes + chunk - 1) / chunk);
-            g.units_per_block = g.rows * g.chunks_per_run;
-            g.unit_begin = upb;
-            upb += g.units_per_block;
-            bytes_per_block += (int64_t)g.run_bytes * g.rows;
-            p.seg[p.nseg++] = g;
-        }
-    }
-    for (int64_t i = 0; i < n_ctx; ++i) {
-        if (ctx_blocks[i] < 0 || ctx_blocks[i] >= src_num_blocks)
-            return fail(KVMIG_EINVAL, "context_block_indexes[%lld] = %lld is outside the context pool (%lld blocks)", (long long)i,
-                        (long long)ctx_blocks[i], (long long)src_num_blocks);
-        if (dec_blocks[i] < 0 || dec_blocks[i] >= shape->num_blocks)
-            return fail(KVMIG_EINVAL, "decoding_block_indexes[%lld] = %lld is outside the decoding pool (%lld blocks)",
-                        (long long)i, (long long)dec_blocks[i], (long long)shape->num_blocks);
-        for (int64_t j = 0; j < i; ++j)   // n <= 4096: a quadratic scan needs no memory
-            if (dec_blocks[j] == dec_blocks[i])
-                return fail(KVMIG_EINVAL, "decoding_block_indexes names block %lld twice", (long long)dec_blocks[i]);
-    }
+    Assembly as;
+    rc = assemble_segments(st, dev, plan, L, H, ctx_tp, ctx_pp, shape, k_cache, v_cache, /*map_missing=*/false, &as);
+    if (rc) return rc;
+    rc = validate_ids(st, ctx_blocks, dec_blocks, n_ctx, as.src_num_blocks, shape->num_blocks);
+    if (rc) return rc;
     if (n_ctx == 0) return 0;
-    if ((int64_t)upb * n_ctx > 0x7fffffff) return fail(KVMIG_ELIMIT, "too many work units for one launch; lower the block count");
+    LaunchShape ls;
+    rc = shape_launch(st, as.align_bits, &ls);
+    if (rc) return rc;
 
-    const int vec = pick_vec(align_bits);
-    int64_t kernel = g_opt.kernel.load();
-    if (kernel == 0) kernel = (vec == 16) ? 2 : 1;
-    if (kernel == 2 && vec != 16) return fail(KVMIG_EINVAL, "the bulk-copy kernel needs 16-byte aligned runs; this shape gives %d", vec);
-    const int64_t stages = std::min<int64_t>(std::max<int64_t>(g_opt.stages.load(), 2), kMaxStages);
-    size_t smem = 0;
-    int64_t ctas_per_sm = g_opt.ctas_per_sm.load();
-    if (kernel == 2) {
-        smem = (size_t)stages * chunk + (size_t)stages * (8 + 8 + 4) + 16;
-        if ((int64_t)smem > st.max_smem_optin) return fail(KVMIG_ELIMIT, "stages x chunk_bytes exceeds the shared memory a CTA may use");
-        if (ctas_per_sm <= 0) {
-            const int64_t ring = stages * chunk, target = 96 * 1024;
-            ctas_per_sm = std::max<int64_t>(1, std::min<int64_t>(8, (target + ring - 1) / ring));
-            ctas_per_sm = std::min<int64_t>(ctas_per_sm, std::max<int64_t>(1, (220 * 1024) / (int64_t)(smem + 1024)));
-        }
-        if ((int)smem > st.bulk_smem_set) {
-            CU_TRY(cudaFuncSetAttribute(kv_migrate_bulk, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            st.bulk_smem_set = (int)smem;
-        }
-    } else if (ctas_per_sm <= 0) {
-        ctas_per_sm = 8;
-    }
+    MigParams p;
+    int64_t bytes_per_block = 0;
+    const unsigned upb = fill_launch(&p, as.segs.data(), (unsigned)as.segs.size(), ls, scratch, &bytes_per_block);
+    if ((int64_t)upb * n_ctx > 0x7fffffff) return fail(KVMIG_ELIMIT, "too many work units for one launch; lower the block count");
 
     // One upload carries the cleared status words and both tables: the array keeps whatever the last
     // call left in it, so everything this launch reads is rewritten first.
@@ -1119,26 +811,9 @@ int migrate_static(int64_t ctx_pp, int64_t ctx_tp, const int64_t* ctx_blocks, in
     g_cnt.memcpy_calls++;
     p.src_ids = scratch + kStaticStatusWords;
     p.dst_ids = scratch + kStaticStatusWords + n_ctx;
-    p.status = scratch;
     p.n_blocks = (unsigned)n_ctx;
-    p.units_per_block = upb;
-    p.wait_limit_ns = (unsigned long long)std::max<int64_t>(1, g_opt.wait_limit_ms.load()) * 1000000ULL;
-    p.chunk_bytes = (unsigned)chunk;
     p.total_units = (unsigned)(n_ctx * upb);
-    const unsigned grid = (unsigned)std::min<int64_t>(p.total_units, (int64_t)st.sm_count * ctas_per_sm);
-    cudaError_t e;
-    if (kernel == 2) {
-        kv_migrate_bulk<<<grid, 32, smem, stream>>>(p, (unsigned)stages, (unsigned)chunk);
-        e = cudaGetLastError();
-    } else {
-        switch (vec) {
-            case 16: e = launch_vec<16>(p, grid, stream); break;
-            case 8: e = launch_vec<8>(p, grid, stream); break;
-            case 4: e = launch_vec<4>(p, grid, stream); break;
-            case 2: e = launch_vec<2>(p, grid, stream); break;
-            default: e = launch_vec<1>(p, grid, stream); break;
-        }
-    }
+    cudaError_t e = launch_device_tables(p, grid_for(st, ls, p.total_units), ls, stream);
     if (e != cudaSuccess) return fail(KVMIG_ECUDA, "launching the migration kernel: %s", cudaGetErrorString(e));
     g_cnt.kernel_launches++;
     int status[4] = {0, 0, 0, 0};
