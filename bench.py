@@ -151,6 +151,8 @@ def cpu_baseline(workload, trace, same_device: bool, seconds: float):
 
     from oracle import kv_oracle as O
 
+    # every host core, also under torchrun (which exports OMP_NUM_THREADS=1 to its ranks)
+    torch.set_num_threads(os.cpu_count() or 1)
     w = workload
     max_pool = 256
     sample = []
