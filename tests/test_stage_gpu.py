@@ -91,6 +91,32 @@ def test_resharded_layouts_end_to_end(name, model):
     run_and_check(model, 16, w.ctx_config(), w.dec_config(), 48, 40, lengths, seed=23)
 
 
+def test_batched_acceptance_equals_one_by_one():
+    """Several requests accepted with one launch per decoding worker leave the
+    same pools as accepting them one awaited call at a time."""
+    capi.reset_registry()
+    model = KVModelConfig(8, 8, 32)
+    ctx, dec = ParallelConfig(4, 0, 1, 0), ParallelConfig(2, 0, 2, 0)
+    ctx_engine, dec_engine = build_stages(model, 16, ctx, dec, 96, 80, seed=25)
+    src_host, dst_host = host_copy(ctx_engine), host_copy(dec_engine)
+    rng = np.random.default_rng(26)
+    batch = []
+    for rid in range(7):
+        req = Request.of_length(rid, int(rng.integers(1, 150)))
+        batch.append(ctx_engine.finish_prefill(req))
+        req.append_token()
+    targets = dec_engine.migrate_blocks_batched(batch)
+    assert [len(t) for t in targets] == [len(m.block_indexes) for m in batch]
+    assert ctx_engine.block_manager.get_num_avail_gpu_blocks() == 96
+    for m, target in zip(batch, targets):
+        for (p, t), (k, v) in dst_host.items():
+            O.migrate_blocks_numpy(src_host, 4, 1, m.block_indexes, 2, t, 2, p, target, k, v, 8, 8)
+    got = host_copy(dec_engine)
+    for key in dst_host:
+        assert np.array_equal(got[key][0], dst_host[key][0]) and np.array_equal(got[key][1], dst_host[key][1]), key
+    assert dec_engine.migrate_blocks_batched([]) == []
+
+
 def test_trace_replay_matches_engine_flow():
     """make_trace() (used by the benchmark) yields the ids the engines yield."""
     w = WORKLOADS["c1"]
