@@ -175,7 +175,7 @@ def cpu_baseline(workload, trace, same_device: bool, seconds: float):
                  for p in range(w.dec_pp) for t in range(w.dec_tp)}
     factor = 2 if same_device else 1
 
-    def one_pass():
+    def one_pass(migrate):
         moved = 0
         for item in sample:
             src, dst = remap(item.src_blocks), remap(item.dst_blocks)
@@ -187,24 +187,37 @@ def cpu_baseline(workload, trace, same_device: bool, seconds: float):
                     s2.append(a)
                     d2.append(b)
             for (p, t), (k, v) in dec_pools.items():
-                O.migrate_blocks_torch(ctx_pools, w.ctx_tp, w.ctx_pp, s2, w.dec_tp, t, w.dec_pp, p, d2, k, v,
-                                       w.model.num_layers, w.model.num_kv_heads)
+                migrate(ctx_pools, w.ctx_tp, w.ctx_pp, s2, w.dec_tp, t, w.dec_pp, p, d2, k, v,
+                        w.model.num_layers, w.model.num_kv_heads)
                 moved += len(d2) * w.dec_block_bytes()
         return moved
 
-    one_pass()   # warm-up: page in the pools
-    t0 = time.perf_counter()
-    moved, passes = 0, 0
-    while True:
-        moved += one_pass()
-        passes += 1
-        if time.perf_counter() - t0 >= seconds:
-            break
-    dt_s = time.perf_counter() - t0
-    return {"value": factor * moved / dt_s / 1e9, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
-            "ms_per_sample_pass": dt_s * 1e3 / passes,
-            "sample": f"first {len(sample)} requests of {w.name}, ids folded into {max_pool}-block host pools, "
-                      f"{passes} passes in {dt_s:.1f} s, torch index_select/index_copy_ on {torch.get_num_threads()} threads"}
+    def timed_passes(fn, budget):
+        one_pass(fn)   # warm-up: page in the pools
+        t0 = time.perf_counter()
+        moved, passes = 0, 0
+        while True:
+            moved += one_pass(fn)
+            passes += 1
+            if time.perf_counter() - t0 >= budget:
+                break
+        return moved, passes, time.perf_counter() - t0
+
+    moved, passes, dt_s = timed_passes(O.migrate_blocks_torch, seconds)
+    out = {"value": factor * moved / dt_s / 1e9, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
+           "ms_per_sample_pass": dt_s * 1e3 / passes,
+           "sample": f"first {len(sample)} requests of {w.name}, ids folded into {max_pool}-block host pools, "
+                     f"{passes} passes in {dt_s:.1f} s, torch index_select/index_copy_ on {torch.get_num_threads()} threads"}
+    # the same semantics as plain C (one memcpy per run, OpenMP over blocks x layers): a stronger CPU arm, for context
+    try:
+        from oracle import kv_oracle_c as OC
+
+        moved_c, passes_c, dt_c = timed_passes(OC.migrate_blocks_c, max(2.0, seconds / 4))
+        out["c_openmp"] = {"value": factor * moved_c / dt_c / 1e9, "unit": UNIT, "cores": os.cpu_count(),
+                           "sample": f"same sample, {passes_c} passes in {dt_c:.1f} s, oracle/kv_oracle.c"}
+    except Exception as e:   # gcc missing on the box: the torch arm stands alone
+        out["c_openmp"] = {"unavailable": str(e)[:200]}
+    return out
 
 
 # ----------------------------------------------------------------------------------------------

@@ -17,11 +17,15 @@ DIGESTS = {row["name"]: row["sha256"] for row in json.loads((GOLDEN / "migrate_c
 
 
 @pytest.mark.parametrize("case", gen.CASES, ids=[c[0] for c in gen.CASES])
-def test_oracle_reproduces_committed_digests(case):
+@pytest.mark.parametrize("form", ["numpy", "c"])
+def test_oracle_reproduces_committed_digests(case, form):
+    from oracle import kv_oracle_c as OC
+
+    fn = O.migrate_blocks_numpy if form == "numpy" else OC.migrate_blocks_c
     name, L, H, (ctp, cpp), (dtp, dpp), *_ = case
     ctx, dec, src, dst = gen.build(case)
     for (p, t), (k, v) in dec.items():
-        O.migrate_blocks_numpy(ctx, ctp, cpp, src, dtp, t, dpp, p, dst, k, v, L, H)
+        fn(ctx, ctp, cpp, src, dtp, t, dpp, p, dst, k, v, L, H)
     assert gen.digest(dec) == DIGESTS[name]
 
 

@@ -7,6 +7,7 @@ import pytest
 import torch
 
 from oracle import kv_oracle as O
+from oracle import kv_oracle_c as OC
 
 LAYOUTS = [
     # L, H, (ctx_tp, ctx_pp), (dec_tp, dec_pp)
@@ -45,7 +46,7 @@ def test_three_statements_agree(L, H, ctx, dec):
             init_k = rng.integers(-2**15, 2**15, size=shape, dtype=np.int16)
             init_v = rng.integers(-2**15, 2**15, size=shape, dtype=np.int16)
             outs = []
-            for fn in (O.migrate_blocks_elementwise, O.migrate_blocks_numpy):
+            for fn in (O.migrate_blocks_elementwise, O.migrate_blocks_numpy, OC.migrate_blocks_c):
                 k, v = init_k.copy(), init_v.copy()
                 fn(pools, ctx_tp, ctx_pp, src, dec_tp, t, dec_pp, p, dst, k, v, L, H)
                 outs.append((k, v))
@@ -123,3 +124,23 @@ def test_swap_oracle_directions_and_order():
     assert not np.array_equal(h_v, h_v0)
     with pytest.raises(ValueError):
         O.swap_numpy([0], [], True, g_k, g_v, h_k, h_v)
+
+
+def test_c_oracle_swap_and_refusals_agree_with_numpy():
+    rng = np.random.default_rng(2)
+    pools = [rng.integers(-2**15, 2**15, size=(n, 2, 3, 4, 8), dtype=np.int16) for n in (6, 6, 4, 4)]
+    a = [p.copy() for p in pools]
+    b = [p.copy() for p in pools]
+    for src, dst, is_in in (([5, 2], [0, 3], False), ([0, 3], [1, 1], True), ([], [], True)):
+        O.swap_numpy(src, dst, is_in, *a)
+        OC.swap_c(src, dst, is_in, *b)
+    for x, y in zip(a, b):
+        assert np.array_equal(x, y)
+    with pytest.raises(ValueError):
+        OC.swap_c([0], [], True, *b)
+    k = np.zeros((2, 2, 2, 1, 1), dtype=np.int16)
+    ctx = make_pools(rng, 2, 2, 2, 1, 1, 1, 1)
+    with pytest.raises(ValueError):
+        OC.migrate_blocks_c(ctx, 1, 1, [0, 1], 1, 0, 1, 0, [0], k, k.copy(), 2, 2)
+    with pytest.raises(ValueError):
+        OC.migrate_blocks_c(ctx, 1, 1, [0], 3, 0, 1, 0, [0], k, k.copy(), 2, 2)
