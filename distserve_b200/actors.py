@@ -22,7 +22,7 @@ import os
 import threading
 import traceback
 from concurrent.futures import Future
-from typing import Any, Callable, Dict, List, Optional
+from typing import Callable, Dict, List, Optional
 
 _CTX = mp.get_context("spawn")
 

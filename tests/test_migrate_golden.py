@@ -4,7 +4,6 @@ import importlib.util
 import json
 from pathlib import Path
 
-import numpy as np
 import pytest
 
 from oracle import kv_oracle as O
