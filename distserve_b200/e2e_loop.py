@@ -242,8 +242,92 @@ def _run(gpus, steps, rate, workload, weight_gb, pool_blocks, seed, time_scale, 
     }
 
 
+def run_swap(steps: int = 300, weight_gb: float = 6.7, workload: str = "c5", pool_blocks: int = 1024,
+             request_blocks: int = 32, every: int = 10, seed: int = 11) -> dict:
+    """Decode steps with a request swapped out to pinned host memory and back in every `every` steps, the
+    way the decoding scheduler does under memory pressure (distserve/decoding_stage_scheduler.py:183-223 via
+    distserve/block_manager.py:288-315, which fires the copies and never awaits them).
+
+    * ``awaited``    — the loop waits for each swap before the next step (what a blocking copy would cost);
+    * ``overlapped`` — the copies run on the worker's swap streams beside the steps; as in the reference,
+      the swapped-in request is in the very next batch, whose step therefore waits for the swap-in
+      (``prepare_step`` makes the compute stream wait for it), so only swap-outs are hidden;
+    * ``deferred``   — as above, but the request rejoins the batch at the first step boundary at which its
+      swap-in event has completed, so swap-ins are hidden too.
+    Returns the loop times and the swapped data's integrity check."""
+    load_ops()
+    from .block_manager import BlockManager
+
+    with torch.cuda.device(0):
+        w = WORKLOADS[workload]
+        model = KVModelConfig(w.model.num_layers, w.model.num_kv_heads // w.dec_tp, w.model.head_dim)
+        cache = CacheConfig(w.block_size, 1 << 20)
+        worker = KVWorker(0, "decoding", model, cache, ParallelConfig(), device=0)
+        worker.init_kvcache_and_swap(pool_blocks, 4 * request_blocks)
+        worker.k_cache.normal_()
+        worker.v_cache.normal_()
+        bm = BlockManager("decoding", pool_blocks, 4 * request_blocks, model, ParallelConfig(), cache,
+                          lambda name, *args: [getattr(worker, name)(*args)])
+        req = Request.of_length(0, request_blocks * w.block_size)
+        bm.allocate_blocks(req)
+        first_ids = list(bm.get_block_table(0))
+        want_k, want_v = worker.k_cache[first_ids].clone(), worker.v_cache[first_ids].clone()
+        decoder = StandInDecoder(torch.device("cuda", 0), int(weight_gb * 1e9))
+        compute = torch.cuda.current_stream()
+        swap_bytes = 2 * request_blocks * model.block_bytes(ParallelConfig(), w.block_size)
+
+        def loop(mode: str) -> float:
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            away = False
+            rejoin_pending = False
+            for step in range(steps):
+                if mode != "decode_only" and step % every == every - 1:
+                    if not away:
+                        bm.swap_out_requests([req])
+                        if mode == "awaited":
+                            worker.wait_for_all_swap_out()
+                    else:
+                        bm.swap_in_requests([req])
+                        if mode == "awaited":
+                            worker.wait_for_all_swap_in()
+                        if mode == "deferred":
+                            rejoin_pending = True
+                        else:
+                            worker.prepare_step([0])       # the request's next step waits for its swap-in
+                    away = not away
+                if rejoin_pending and worker.swap_event_table[0].query():
+                    worker.prepare_step([0])               # already complete: rejoins without stalling the step
+                    rejoin_pending = False
+                decoder.step()
+                compute.synchronize()
+            if away:
+                bm.swap_in_requests([req])
+                worker.prepare_step([0])
+            worker.wait_for_all_swap_out()
+            worker.wait_for_all_swap_in()
+            torch.cuda.synchronize()
+            return (time.perf_counter() - t0) * 1e3
+
+        times = {}
+        for mode in ("decode_only", "awaited", "overlapped", "deferred") * 2:
+            t = loop(mode)
+            times[mode] = min(t, times.get(mode, t))
+        ids = list(bm.get_block_table(0))
+        intact = bool(torch.equal(worker.k_cache[ids], want_k) and torch.equal(worker.v_cache[ids], want_v))
+        n = max(1, steps // every)
+        return {"steps": steps, "swap_every_steps": every, "bytes_per_swap": swap_bytes, "swaps": n,
+                "loop_ms": times,
+                "added_ms_per_swap": {m: (times[m] - times["decode_only"]) / n for m in ("awaited", "overlapped", "deferred")},
+                "hidden_fraction": {m: max(0.0, 1.0 - (times[m] - times["decode_only"]) /
+                                           max(1e-9, times["awaited"] - times["decode_only"]))
+                                    for m in ("overlapped", "deferred")},
+                "data_intact_after_round_trips": intact}
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
+    ap.add_argument("--swap", action="store_true", help="measure swap-out/in beside decode steps instead of migration")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=400)
     ap.add_argument("--rate", type=float, default=4.0)
@@ -253,6 +337,9 @@ def main() -> None:
     ap.add_argument("--opt", action="append", default=None, metavar="NAME=VALUE",
                     help="kernel option for the overlapped run (replaces the side-by-side defaults)")
     args = ap.parse_args()
+    if args.swap:
+        print(json.dumps(run_swap(steps=args.steps, weight_gb=args.weight_gb, workload=args.workload)))
+        return
     options = None if args.opt is None else {k: int(v) for k, v in (pair.split("=") for pair in args.opt)}
     print(json.dumps(run(args.gpus, args.steps, args.rate, args.workload, args.weight_gb, time_scale=args.time_scale,
                          overlapped_options=options)))

@@ -19,3 +19,9 @@ def test_overlapped_loop_is_correct_and_no_slower_than_serial():
     assert loop["serial"] >= loop["decode_only"] * 0.98
     assert loop["overlapped"] <= loop["serial"] * 1.05
     capi.reset_registry()
+
+
+def test_swaps_beside_decode_steps_keep_the_data_and_cost_less_than_waiting():
+    out = e2e_loop.run_swap(steps=60, weight_gb=1.0, pool_blocks=256, request_blocks=16, every=5)
+    assert out["data_intact_after_round_trips"] is True
+    assert out["loop_ms"]["overlapped"] <= out["loop_ms"]["awaited"] * 1.05
