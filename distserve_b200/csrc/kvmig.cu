@@ -77,14 +77,14 @@ int64_t handle_checksum(const int64_t* w) {
     return (int64_t)h;
 }
 
-// Defaults from sweeps on B200: 8 KiB chunks, a 3-stage ring and 4 CTAs per SM (96 KiB in flight per SM,
-// 592 CTAs).  With CTAs drawing units on demand and consecutive launches overlapping, same-GPU copies of
-// OPT-13B-shaped blocks run at 6.8 TB/s for any setting from 64 to 192 KiB in flight per SM; awaited single
-// calls, which pay their own ramp-up and tail, were fastest around 96 KiB.  Anything from 16 KiB in flight per
-// SM upward saturates NVLink.
+// Defaults from sweeps on B200: 16 KiB chunks, a 3-stage ring and 2 CTAs per SM (96 KiB in flight per SM,
+// 296 CTAs), CTAs drawing two consecutive units (32 KiB) per visit to the work counter.  With consecutive
+// launches overlapping, same-GPU copies of OPT-13B-shaped blocks run at 6.8-6.9 TB/s for any setting from 64 to
+// 192 KiB in flight per SM; awaited single calls, which pay their own ramp-up and tail, were fastest around
+// 96 KiB.  Anything from 16 KiB in flight per SM upward saturates NVLink.
 struct Options {
-    std::atomic<int64_t> kernel{0}, chunk_bytes{8192}, stages{3}, ctas_per_sm{0}, inline_tables{1}, overlap_launches{1}, max_ctas{0}, l2_hint{0},
-        dynamic_units{1}, wait_limit_ms{2000}, lose_unit_plus1{0};
+    std::atomic<int64_t> kernel{0}, chunk_bytes{16384}, stages{3}, ctas_per_sm{0}, inline_tables{1}, overlap_launches{1}, max_ctas{0}, l2_hint{0},
+        dynamic_units{1}, wait_limit_ms{2000}, lose_unit_plus1{0}, unit_batch{0};
 };
 Options g_opt;
 
@@ -664,7 +664,8 @@ int enqueue_migration(int64_t ctx_pp, int64_t ctx_tp, const int64_t* ctx_blocks,
             p.batch = 1;
             if (ls.kernel == 2 && g_opt.dynamic_units.load() != 0 && launch_index < kWorkPairs && p.total_units >= 4u * grid) {
                 p.work = sl.work + 2 * launch_index;
-                p.batch = p.total_units >= 32u * grid ? 4u : (p.total_units >= 8u * grid ? 2u : 1u);
+                p.batch = p.total_units >= 8u * grid ? 2u : 1u;
+                if (const int64_t fixed = g_opt.unit_batch.load(); fixed > 0) p.batch = (unsigned)fixed;
             }
             ++launch_index;
             cudaError_t e;
@@ -1036,6 +1037,7 @@ static std::atomic<int64_t>* option_slot(const char* name) {
     if (!std::strcmp(name, "l2_hint")) return &g_opt.l2_hint;
     if (!std::strcmp(name, "dynamic_units")) return &g_opt.dynamic_units;
     if (!std::strcmp(name, "wait_limit_ms")) return &g_opt.wait_limit_ms;
+    if (!std::strcmp(name, "unit_batch")) return &g_opt.unit_batch;
     if (!std::strcmp(name, "lose_unit_plus1")) return &g_opt.lose_unit_plus1;
     return nullptr;
 }
