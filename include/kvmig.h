@@ -216,7 +216,10 @@ KVMIG_API int kvmig_swap(const int64_t* source_block_ids, int64_t num_source,
 /*
  * Tuning and introspection (no counterpart in the reference).
  *   options : "kernel" 0 auto | 1 vector loads | 2 bulk-copy pipeline,
- *             "chunk_bytes", "stages", "ctas_per_sm",
+ *             "chunk_bytes" size of one work unit = one shared-memory stage
+ *             (default 16384), "stages" ring depth per CTA (default 3),
+ *             "ctas_per_sm" (default 0 = as many as keep 96 KiB in flight per
+ *             SM: 2 with the defaults),
  *             "inline_tables" 1 = lists of up to 1024 blocks travel in the
  *             kernel parameters instead of a device table (default 1),
  *             "overlap_launches" 1 = a migration whose target blocks are
@@ -226,7 +229,8 @@ KVMIG_API int kvmig_swap(const int64_t* source_block_ids, int64_t num_source,
  *             running beside a decode step leaves the other SMs to it
  *             (default 0 = no cap),
  *             "dynamic_units" 1 = CTAs draw work units from a device counter
- *             instead of a fixed round-robin share (default 1),
+ *             instead of a fixed round-robin share (default 1), "unit_batch"
+ *             units drawn per visit (default 0 = 2 for long launches, else 1),
  *             "l2_hint" bit 0 / bit 1 = evict-first L2 policy on the bulk
  *             loads / stores (default 0),
  *             "wait_limit_ms" longest the copy kernel waits for one of its
