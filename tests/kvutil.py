@@ -9,8 +9,8 @@ import torch
 from distserve_b200 import capi
 from oracle import kv_oracle as O
 
-NP_OF_SIZE = {2: np.int16, 4: np.int32}
-TORCH_OF_SIZE = {2: torch.int16, 4: torch.int32}
+NP_OF_SIZE = {1: np.int8, 2: np.int16, 4: np.int32, 8: np.int64}
+TORCH_OF_SIZE = {1: torch.int8, 2: torch.int16, 4: torch.int32, 8: torch.int64}
 
 
 def host_pool(seed, shape, elem_size=2):

@@ -76,7 +76,8 @@ def test_chunking_does_not_change_the_result(kernel, chunk, stages):
     assert_stage_equals_host(ds)
 
 
-@pytest.mark.parametrize("B,D,elem", [(1, 4, 2), (3, 1, 2), (1, 1, 2), (16, 80, 2), (16, 64, 4), (5, 3, 4)])
+@pytest.mark.parametrize("B,D,elem", [(1, 4, 2), (3, 1, 2), (1, 1, 2), (16, 80, 2), (16, 64, 4), (5, 3, 4),
+                                      (16, 128, 1), (7, 5, 1), (3, 1, 1), (4, 16, 8)])   # 1-byte (fp8-sized) and 8-byte values too
 def test_odd_shapes_fall_back_to_narrower_vectors(B, D, elem):
     """Slabs that are not multiples of 16 bytes cannot use the bulk kernel;
     automatic selection must still be bit-exact."""
