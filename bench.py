@@ -511,7 +511,7 @@ def main():
         kernel_label = "kv_migrate_bulk / kv_migrate_bulk_inline"
     if same_device:
         peak, peak_kind = hbm_peak()
-        # ncu on a small case of this kernel (profiles/): DRAM reads equal the algorithmic read bytes, DRAM
+        # ncu on a small case of this kernel: DRAM reads equal the algorithmic read bytes, DRAM
         # writes fall short of the algorithmic write bytes by the ~48.8 MB still dirty in L2 at kernel end.
         alg = factor * worst[2]
         traffic = alg / 2 + max(0.0, alg / 2 - 48.8e6) if capi.get_option("kernel") in (0, 2) else None

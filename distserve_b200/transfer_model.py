@@ -1,5 +1,5 @@
 """Cost model of one KV migration, fitted to the measurements of this library
-on B200 (profiles/): what a placement search or a simulator needs in order to
+on B200: what a placement search or a simulator needs in order to
 charge for the transfer.  The reference's simulator charges nothing for it
 (simdistserve/base/worker.py:264-279 moves a request from prefill to decode
 with no delay; the only KV-related helper is a size estimate,

@@ -1,5 +1,5 @@
-"""The transfer-cost model against what was measured on B200 (figures copied
-from profiles/bench__all_workloads__n1_to_n8.md)."""
+"""The transfer-cost model against what the benchmark measured on B200
+(median awaited-call latency and back-to-back throughput per workload)."""
 import pytest
 
 from distserve_b200 import transfer_model as T
