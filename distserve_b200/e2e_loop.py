@@ -296,7 +296,7 @@ def run_swap(steps: int = 300, weight_gb: float = 6.7, workload: str = "c5", poo
                         else:
                             worker.prepare_step([0])       # the request's next step waits for its swap-in
                     away = not away
-                if rejoin_pending and worker.swap_event_table[0].query():
+                if rejoin_pending and worker.swap_finished(0):
                     worker.prepare_step([0])               # already complete: rejoins without stalling the step
                     rejoin_pending = False
                 decoder.step()

@@ -10,8 +10,11 @@ Calls go through ``torch.ops.block_migration_ops.*`` / ``torch.ops.swapping_ops.
 this package's shim registers.  Without the built libraries or without a CUDA
 device construction fails; there is no CPU fallback.
 
-Two deliberate differences from the reference worker, both in the swap event
+Deliberate differences from the reference worker, all in the swap event
 protocol (design note at distserve/block_manager.py:211-286):
+* swap events are numbered per direction and the highest finished number is
+  remembered, so waits on swaps already known to be over are skipped — the
+  optimisation the note leaves for later (277-285);
 * the per-request event is recorded *after* the copies are enqueued, so that
   waiting on it really waits for them (the reference records it before,
   distserve/worker.py:286-287 vs 302-311);
@@ -35,6 +38,17 @@ def _request_id(item) -> int:
     return item if isinstance(item, int) else item.request_id
 
 
+class _SwapMark:
+    """The event recorded after a swap, numbered within its direction.  Swaps of one direction run in
+    order on one stream, so once mark n is known to have completed, every mark <= n has too — the
+    shortcut the reference's design note proposes (distserve/block_manager.py:277-285)."""
+
+    __slots__ = ("event", "seq", "is_swap_in")
+
+    def __init__(self, event, seq: int, is_swap_in: bool) -> None:
+        self.event, self.seq, self.is_swap_in = event, seq, is_swap_in
+
+
 class KVWorker:
     def __init__(self, worker_id: int, stage, model_config: KVModelConfig, cache_config: CacheConfig,
                  parallel_config: ParallelConfig = ParallelConfig(), device: Optional[int] = None) -> None:
@@ -54,9 +68,11 @@ class KVWorker:
         with torch.cuda.device(self.device):
             self.swap_in_stream = torch.cuda.Stream()
             self.swap_out_stream = torch.cuda.Stream()
-        self.swap_event_table: Dict[int, torch.cuda.Event] = {}
+        self.swap_event_table: Dict[int, _SwapMark] = {}
         self.latest_swap_in_event: Optional[torch.cuda.Event] = None
         self.latest_swap_out_event: Optional[torch.cuda.Event] = None
+        self._swaps_issued = {True: 0, False: 0}        # per direction (is_swap_in)
+        self._swaps_known_done = {True: 0, False: 0}    # highest mark known to have completed
         self.blocked_swapping_time = 0.0
 
     # --- pools and handles ---------------------------------------------------------------
@@ -152,19 +168,37 @@ class KVWorker:
             stream.wait_stream(torch.cuda.current_stream())
             for rid in ids:
                 earlier = self.swap_event_table.get(rid)
-                if earlier is not None:
-                    earlier.wait(stream)
+                if earlier is not None and not self._swap_done(earlier):
+                    earlier.event.wait(stream)
             with torch.cuda.stream(stream):
                 torch.ops.swapping_ops.swap(source_block_ids, target_block_ids, is_swap_in,
                                             self.k_cache, self.v_cache, self.k_swap, self.v_swap)
             event = torch.cuda.Event()
             event.record(stream)
+            self._swaps_issued[is_swap_in] += 1
+            mark = _SwapMark(event, self._swaps_issued[is_swap_in], is_swap_in)
             for rid in ids:
-                self.swap_event_table[rid] = event
+                self.swap_event_table[rid] = mark
             if is_swap_in:
                 self.latest_swap_in_event = event
             else:
                 self.latest_swap_out_event = event
+
+    def _swap_done(self, mark: _SwapMark) -> bool:
+        """True if the swap behind `mark` has finished; remembers the highest finished mark per direction so
+        that later questions about older swaps need no CUDA call at all."""
+        if mark.seq <= self._swaps_known_done[mark.is_swap_in]:
+            return True
+        if mark.event.query():
+            self._swaps_known_done[mark.is_swap_in] = mark.seq
+            return True
+        return False
+
+    def swap_finished(self, request_id) -> bool:
+        """Has the last swap of this request completed (or was there none)?  Lets a scheduler put a
+        swapped-in request back into the batch only when that costs the step nothing."""
+        mark = self.swap_event_table.get(_request_id(request_id))
+        return mark is None or self._swap_done(mark)
 
     def prepare_step(self, request_ids: Iterable[int]) -> None:
         """What ``step`` does before the forward (distserve/worker.py:205-211):
@@ -172,9 +206,9 @@ class KVWorker:
         with torch.cuda.device(self.device):
             current = torch.cuda.current_stream()
             for rid in request_ids:
-                event = self.swap_event_table.pop(_request_id(rid), None)
-                if event is not None:
-                    event.wait(current)
+                mark = self.swap_event_table.pop(_request_id(rid), None)
+                if mark is not None and not self._swap_done(mark):
+                    mark.event.wait(current)
 
     def clear_request_resource(self, request_id: int) -> None:
         self.swap_event_table.pop(request_id, None)
@@ -187,11 +221,13 @@ class KVWorker:
         if self.latest_swap_in_event is not None:
             self.latest_swap_in_event.synchronize()
             self.latest_swap_in_event = None
+            self._swaps_known_done[True] = self._swaps_issued[True]
 
     def wait_for_all_swap_out(self) -> None:
         if self.latest_swap_out_event is not None:
             self.latest_swap_out_event.synchronize()
             self.latest_swap_out_event = None
+            self._swaps_known_done[False] = self._swaps_issued[False]
 
 
 # Same name as the reference class for code written against it.

@@ -143,6 +143,9 @@ def test_worker_passes_the_reference_arguments(golden_dir, monkeypatch):
         def wait(self, stream=None):
             pass
 
+        def query(self):
+            return False
+
     real_empty = torch.empty
     monkeypatch.setattr(torch.ops, "block_migration_ops", Recorder("block_migration_ops"), raising=False)
     monkeypatch.setattr(torch.ops, "swapping_ops", Recorder("swapping_ops"), raising=False)
@@ -163,6 +166,7 @@ def test_worker_passes_the_reference_arguments(golden_dir, monkeypatch):
         w.device = "meta"
         w.swap_in_stream, w.swap_out_stream = FakeStream(), FakeStream()
         w.swap_event_table, w.latest_swap_in_event, w.latest_swap_out_event = {}, None, None
+        w._swaps_issued, w._swaps_known_done = {True: 0, False: 0}, {True: 0, False: 0}
         ctx_tp, ctx_pp = case["ctx"]
         returned = w.init_kvcache_and_swap(32, 8)
         table = [[([1000 + p * 10 + t], [2000 + p * 10 + t]) for t in range(ctx_tp)] for p in range(ctx_pp)]
@@ -173,3 +177,77 @@ def test_worker_passes_the_reference_arguments(golden_dir, monkeypatch):
         w.swap_blocks([11], [0, 1], [7, 8], True)
         assert [list(h) for h in returned] == case["init_returned"]
         assert recorded == case["calls"], case["model"]
+
+
+def test_swap_waits_are_skipped_once_a_later_swap_is_known_to_be_done(monkeypatch):
+    """Swaps of one direction run in order on one stream: when mark n is known to have finished, questions
+    about marks <= n must not touch CUDA any more (the shortcut of distserve/block_manager.py:277-285)."""
+    import distserve_b200.worker as W
+
+    log = []
+
+    class Ctx:
+        def __enter__(self):
+            return self
+
+        def __exit__(self, *a):
+            return False
+
+    class FakeStream(Ctx):
+        def wait_stream(self, other):
+            pass
+
+    class FakeEvent:
+        finished = set()
+
+        def __init__(self):
+            self.id = len(log)
+
+        def record(self, stream=None):
+            log.append(("record", id(self)))
+
+        def wait(self, stream=None):
+            log.append(("wait", id(self)))
+
+        def query(self):
+            log.append(("query", id(self)))
+            return id(self) in FakeEvent.finished
+
+        def synchronize(self):
+            log.append(("synchronize", id(self)))
+
+    class Ops:
+        def swap(self, *args):
+            pass
+
+    monkeypatch.setattr(torch.ops, "swapping_ops", Ops(), raising=False)
+    monkeypatch.setattr(W.torch.cuda, "device", lambda d: Ctx())
+    monkeypatch.setattr(W.torch.cuda, "stream", lambda s: Ctx())
+    monkeypatch.setattr(W.torch.cuda, "current_stream", lambda *a: FakeStream())
+    monkeypatch.setattr(W.torch.cuda, "Event", FakeEvent)
+    w = object.__new__(W.KVWorker)
+    w.device = "meta"
+    w.k_cache = w.v_cache = w.k_swap = w.v_swap = None
+    w.swap_in_stream, w.swap_out_stream = FakeStream(), FakeStream()
+    w.swap_event_table, w.latest_swap_in_event, w.latest_swap_out_event = {}, None, None
+    w._swaps_issued, w._swaps_known_done = {True: 0, False: 0}, {True: 0, False: 0}
+
+    for rid in (1, 2, 3):
+        w.swap_blocks([rid], [rid], [rid], False)                  # three swap-outs, marks 1..3
+    marks = {rid: w.swap_event_table[rid] for rid in (1, 2, 3)}
+    assert [m.seq for m in marks.values()] == [1, 2, 3]
+    assert w.swap_finished(2) is False                              # queried, not finished
+    FakeEvent.finished.add(id(marks[3].event))
+    assert w.swap_finished(3) is True                               # one query: mark 3 is over ...
+    log.clear()
+    assert w.swap_finished(1) is True and w.swap_finished(2) is True   # ... so 1 and 2 are, without any CUDA call
+    w.prepare_step([1, 2])
+    assert log == []
+    w.swap_blocks([9], [0], [0], True)                              # the other direction keeps its own numbering
+    assert w.swap_event_table[9].seq == 1 and w.swap_finished(9) is False
+    w.prepare_step([9])
+    assert ("wait", id(w.latest_swap_in_event)) in log
+    w.swap_blocks([7], [1], [1], True)
+    w.wait_for_all_swap_in()
+    log.clear()
+    assert w.swap_finished(7) is True and log == []                 # the flush marked everything issued as done
