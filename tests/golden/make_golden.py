@@ -13,6 +13,9 @@ on this path:
 * block_manager.json  — every block table and every worker call produced by
                         the reference BlockManager over a seeded sequence of
                         allocate / extend / free / swap-out / swap-in steps;
+* scheduler.json      — every decision of the reference decoding-stage scheduler
+                        (batches, acceptances = migrations, swap-outs and
+                        swap-ins) over seeded arrival traces;
 * worker_calls.json   — the exact positional arguments the reference
                         ParaWorker passes to the four native operators.
 
@@ -277,12 +280,92 @@ def golden_worker_calls(tmp: str):
     return cases
 
 
+SCHEDULER_SCENARIOS = [
+    # seed, gpu_blocks, cpu_blocks, block_size, max_batch_size, max_tokens_per_batch, threshold, iterations
+    (11, 48, 64, 16, 8, 64, 0.25, 260),
+    (12, 96, 96, 8, 16, 32, 0.10, 260),
+    (13, 400, 64, 16, 4, 8, 0.05, 200),
+]
+
+
+def golden_scheduler(tmp: str):
+    """Drive the reference decoding-stage scheduler the way DecodingStageLLMEngine._step does
+    (get_next_batch, allocate, one token per request, pop finished, free, post_process) over a seeded
+    arrival trace, and record every decision."""
+    import asyncio
+
+    from distserve.block_manager import BlockManager
+    from distserve.config import CacheConfig, DecodingStageSchedConfig, ModelConfig, ParallelConfig
+    from distserve.decoding_stage_scheduler import DecodingStageFCFSScheduler
+    from distserve.request import MigratingRequest, Request, SamplingParams
+    from distserve.utils import Stage
+
+    mc = ModelConfig(write_hf_dir(tmp, "opt-125m"), None)
+
+    async def run(seed, gpu_blocks, cpu_blocks, block_size, max_bs, max_tok, thr, iters):
+        rng = random.Random(seed)
+        swaps, migrated = [], []
+
+        def record(name, *args):
+            if name == "swap_blocks":
+                reqs, src, dst, is_in = args
+                swaps.append([[r.request_id for r in reqs], list(src), list(dst), bool(is_in)])
+
+        pc = ParallelConfig()
+        bm = BlockManager(Stage.DECODING, gpu_blocks, cpu_blocks, mc, pc, CacheConfig(block_size, 256), record)
+
+        async def migrate(m):
+            req = m.req
+            kept = (req.generated_tokens, req.generated_token_ids)
+            req.generated_tokens, req.generated_token_ids = [], []
+            bm.allocate_blocks(req)
+            req.generated_tokens, req.generated_token_ids = kept
+            migrated.append(req.request_id)
+
+        sched = DecodingStageFCFSScheduler(DecodingStageSchedConfig("fcfs", max_bs, max_tok, waiting_block_prop_threshold=thr),
+                                           pc, bm, migrate)
+        steps, next_id = [], 0
+        for _ in range(iters):
+            swaps.clear()
+            migrated.clear()
+            arrivals = []
+            for _ in range(rng.choice([0, 0, 0, 1, 1, 2])):
+                n, mt = rng.randint(4, 12 * block_size), rng.randint(2, 40)
+                req = Request(0.0, next_id, "", [0] * n, SamplingParams(max_tokens=mt))
+                req.add_generated_token("", 0)        # the token prefill produced
+                await sched.add_request(MigratingRequest(req, list(range(-(-n // block_size))), pc))
+                arrivals.append([next_id, n, mt])
+                next_id += 1
+            batch = sched.get_next_batch()
+            batch_ids = batch.get_request_ids()
+            finished = []
+            if len(batch):
+                bm.allocate_blocks_batched(batch)
+                for r in batch.requests:
+                    r.add_generated_token("", 0)
+                finished = sched.pop_finished_requests()
+                bm.free_blocks_batched(finished)
+            swaps_in_batching = [list(x) for x in swaps]
+            await sched.post_process()
+            steps.append(dict(arrivals=arrivals, batch=batch_ids, finished=[r.request_id for r in finished],
+                              swaps=swaps_in_batching, accepted=list(migrated),
+                              unaccepted=[len(sched.unaccepted_queue)] + [m.req.request_id for m in sched.unaccepted_queue[:2]],
+                              waiting=[r.request_id for r in sched.waiting_queue],
+                              swapped=[r.request_id for r in sched.swapped_queue],
+                              avail=[bm.get_num_avail_gpu_blocks(), bm.get_num_avail_cpu_blocks()],
+                              digest=state_digest(bm)))
+        return dict(seed=seed, gpu_blocks=gpu_blocks, cpu_blocks=cpu_blocks, block_size=block_size, max_batch_size=max_bs,
+                    max_tokens_per_batch=max_tok, threshold=thr, steps=steps)
+
+    return [asyncio.run(run(*sc)) for sc in SCHEDULER_SCENARIOS]
+
+
 def main():
     ref_root = sys.argv[1] if len(sys.argv) > 1 else str(ROOT.parent / "reference")   # a checkout beside this repo
     import_reference(ref_root)
     with tempfile.TemporaryDirectory() as tmp:
         for name, fn in (("geometry", golden_geometry), ("block_manager", golden_block_manager),
-                         ("worker_calls", golden_worker_calls)):
+                         ("scheduler", golden_scheduler), ("worker_calls", golden_worker_calls)):
             data = fn(tmp)
             with open(HERE / f"{name}.json", "w") as f:
                 json.dump(data, f, separators=(",", ":"))

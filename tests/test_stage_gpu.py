@@ -178,3 +178,85 @@ def test_two_processes_share_pools_through_ipc_handles():
         proc.join(30)
         if proc.is_alive():
             proc.kill()
+
+
+def test_scheduler_driven_loop_keeps_every_request_intact():
+    """The whole decoding-stage control path over real pools: the scheduler
+    accepts requests (batched migration), swaps them out under block pressure
+    and back in, requests finish and their blocks are recycled.  At every
+    checkpoint each live request's prompt blocks — on the GPU or in the pinned
+    host pool — must equal what the context stage held for it."""
+    import random
+
+    from distserve_b200.block_manager import BlockLocation
+    from distserve_b200.scheduler import DecodingStageFCFSScheduler, DecodingStageSchedConfig
+
+    capi.reset_registry()
+    model, block_size = KVModelConfig(4, 4, 32), 16
+    pc = ParallelConfig()
+    cache = CacheConfig(block_size, 1 << 20)
+    ctx_w = KVWorker(0, "context", model, cache, pc)
+    dec_w = KVWorker(1, "decoding", model, cache, pc)
+    ctx_engine = ContextStageEngine(model, pc, cache, [[ctx_w]])
+    dec_engine = DecodingStageEngine(model, pc, cache, [[dec_w]], clear_migrated_blocks_callback=ctx_engine.clear_migrated_blocks)
+    handles = ctx_engine.init_kvcache(256, 1)
+    dec_engine.init_kvcache(48, 64)
+    g = torch.Generator(device="cuda").manual_seed(77)
+    for pool in (ctx_w.k_cache, ctx_w.v_cache):
+        pool.copy_(torch.randn(pool.shape, device="cuda", generator=g).half())
+    dec_w.k_cache.zero_()
+    dec_w.v_cache.zero_()
+    dec_engine.register_kvcache_mem_handles(pc, handles)
+    bm = dec_engine.block_manager
+    sched = DecodingStageFCFSScheduler(DecodingStageSchedConfig("fcfs", 8, 64, 0.25), pc, bm, dec_engine.migrate_blocks,
+                                       dec_engine.migrate_blocks_batched)
+    rng = random.Random(11)
+    expected, live, next_id, swaps_seen = {}, {}, 0, 0
+
+    def check_all():
+        dec_w.wait_for_all_swap_out()
+        dec_w.wait_for_all_swap_in()
+        torch.cuda.synchronize()
+        for rid, req in live.items():
+            if rid not in bm.block_table:
+                continue                                     # not accepted yet
+            n = -(-req.get_input_len() // block_size)
+            ids = bm.get_block_table(rid)[:n]
+            want_k, want_v = expected[rid]
+            if bm.get_location(rid) == BlockLocation.GPU:
+                got_k, got_v = dec_w.k_cache[ids].cpu(), dec_w.v_cache[ids].cpu()
+            else:
+                got_k, got_v = dec_w.k_swap[ids], dec_w.v_swap[ids]
+            assert torch.equal(got_k, want_k) and torch.equal(got_v, want_v), f"request {rid} lost its KV"
+
+    for it in range(160):
+        for _ in range(rng.choice([0, 0, 0, 1, 1, 2])):
+            n, mt = rng.randint(4, 12 * block_size), rng.randint(2, 40)
+            if ctx_engine.block_manager.get_num_avail_gpu_blocks() < -(-n // block_size):
+                continue
+            req = Request(next_id, [0] * n, max_tokens=mt)
+            m = ctx_engine.finish_prefill(req)
+            expected[next_id] = (ctx_w.k_cache[m.block_indexes].cpu(), ctx_w.v_cache[m.block_indexes].cpu())
+            req.add_generated_token()
+            sched.add_request(m)
+            live[next_id] = req
+            next_id += 1
+        before = len(bm.swapping_gpu_blocks_list) + len(bm.swapping_cpu_blocks_list)
+        batch = sched.get_next_batch()
+        swaps_seen += (len(bm.swapping_gpu_blocks_list) + len(bm.swapping_cpu_blocks_list)) != before
+        if len(batch):
+            bm.allocate_blocks_batched(batch)
+            dec_w.prepare_step(batch.get_request_ids())
+            for r in batch.requests:
+                r.add_generated_token()
+            finished = sched.pop_finished_requests()
+            bm.free_blocks_batched(finished)
+            dec_w.clear_request_resource_batched(finished)
+            for r in finished:
+                live.pop(r.request_id)
+        sched.post_process_batched()
+        if it % 20 == 19:
+            check_all()
+    check_all()
+    assert swaps_seen >= 3 and next_id >= 40
+    assert len(sched.waiting_queue) + sched.get_processing_num_requests() + len(sched.swapped_queue) > 0
