@@ -162,3 +162,72 @@ class DecodingStageFCFSScheduler:
     def __repr__(self) -> str:
         return (f"FCFS(max_batch_size={self.sched_config.max_batch_size}, "
                 f"max_tokens_per_batch={self.sched_config.max_tokens_per_batch})")
+
+
+@dataclass
+class ContextStageSchedConfig:
+    """distserve/config.py ContextStageSchedConfig."""
+
+    policy: str = "fcfs"
+    max_batch_size: int = 256
+    max_tokens_per_batch: int = 8192
+
+
+class ContextStageFCFSScheduler:
+    """The context stage's scheduler, mirror of ``distserve/context_stage_scheduler.py``
+    (ContextStageFCFSScheduler 82-188).  Its tie to the migration path: a request that finished prefill keeps
+    its blocks — and keeps counting against the block budget of new prefill batches — until the decoding
+    stage has pulled them (``on_request_migrated``), so slow migration throttles prefill."""
+
+    def __init__(self, sched_config: ContextStageSchedConfig, parallel_config: ParallelConfig, block_manager: BlockManager) -> None:
+        assert sched_config.policy == "fcfs", f"can not initialize a FCFS scheduler with policy {sched_config.policy}"
+        self.sched_config = sched_config
+        self.parallel_config = parallel_config
+        self.block_manager = block_manager
+        self.waiting_queue: List[Request] = []
+        self.unaccepted_queue: List[Request] = []      # prefill done, blocks not yet pulled by the decoding stage
+        self.num_on_fly_request_block = 0              # blocks of the batches being prefilled right now
+
+    def _blocks(self, num_tokens: int) -> int:
+        return -(-num_tokens // self.block_manager.cache_config.block_size)
+
+    def add_request(self, request: Request) -> None:
+        self.waiting_queue.append(request)
+
+    def abort_request(self, request_id: int) -> None:
+        for i, request in enumerate(self.waiting_queue):
+            if request.request_id == request_id:
+                del self.waiting_queue[i]
+                return
+
+    def get_next_batch_and_pop(self) -> BatchedRequests:
+        batch = BatchedRequests()
+        held = sum(self._blocks(r.get_input_len()) for r in self.unaccepted_queue) + self.num_on_fly_request_block
+        batch_blocks = 0
+        while self.waiting_queue:
+            request = self.waiting_queue[0]
+            need = self._blocks(request.get_input_len())
+            if not (len(batch) < self.sched_config.max_batch_size
+                    and batch.get_num_input_tokens() + request.get_num_input_tokens() <= self.sched_config.max_tokens_per_batch
+                    and batch_blocks + need + held <= self.block_manager.max_num_gpu_blocks):
+                break
+            batch.add_request(request)
+            batch_blocks += need
+            self.waiting_queue.pop(0)
+        self.num_on_fly_request_block += batch_blocks
+        return batch
+
+    def on_finish_requests(self, batch: BatchedRequests) -> None:
+        for request in batch.requests:
+            if not request.is_finished:
+                self.unaccepted_queue.append(request)
+        self.num_on_fly_request_block -= sum(self._blocks(r.get_input_len()) for r in batch.requests)
+
+    def on_request_migrated(self, migrated_request: MigratingRequest) -> None:
+        for i, request in enumerate(self.unaccepted_queue):
+            if request.request_id == migrated_request.req.request_id:
+                del self.unaccepted_queue[i]
+                return
+
+    def get_num_waiting_requests(self) -> int:
+        return len(self.waiting_queue)

@@ -16,6 +16,8 @@ on this path:
 * scheduler.json      — every decision of the reference decoding-stage scheduler
                         (batches, acceptances = migrations, swap-outs and
                         swap-ins) over seeded arrival traces;
+* context_scheduler.json — prefill batches of the reference context-stage
+                        scheduler while finished requests wait to be migrated;
 * worker_calls.json   — the exact positional arguments the reference
                         ParaWorker passes to the four native operators.
 
@@ -360,12 +362,57 @@ def golden_scheduler(tmp: str):
     return [asyncio.run(run(*sc)) for sc in SCHEDULER_SCENARIOS]
 
 
+def golden_context_scheduler(tmp: str):
+    """The reference context-stage scheduler over a seeded trace: arrivals, prefill batches, and
+    migrations completing a random number of iterations later."""
+    from distserve.block_manager import BlockManager
+    from distserve.config import CacheConfig, ContextStageSchedConfig, ModelConfig, ParallelConfig
+    from distserve.context_stage_scheduler import ContextStageFCFSScheduler
+    from distserve.request import MigratingRequest, Request, SamplingParams
+    from distserve.utils import Stage
+
+    mc = ModelConfig(write_hf_dir(tmp, "opt-125m"), None)
+    out = []
+    for seed, gpu_blocks, block_size, max_bs, max_tok in [(21, 30, 16, 4, 256), (22, 64, 8, 8, 100)]:
+        rng = random.Random(seed)
+        pc = ParallelConfig()
+        bm = BlockManager(Stage.CONTEXT, gpu_blocks, 1, mc, pc, CacheConfig(block_size, 256), lambda *a: None)
+        sched = ContextStageFCFSScheduler(ContextStageSchedConfig("fcfs", max_bs, max_tok), pc, bm)
+        pending, steps, next_id = [], [], 0
+        for it in range(200):
+            arrivals = []
+            for _ in range(rng.choice([0, 1, 1, 2])):
+                n = rng.randint(4, 10 * block_size)
+                sched.add_request(Request(0.0, next_id, "", [0] * n, SamplingParams(max_tokens=rng.choice([1, 8]))))
+                arrivals.append([next_id, n])
+                next_id += 1
+            batch = sched.get_next_batch_and_pop()
+            ids = batch.get_request_ids()
+            for r in batch.requests:
+                r.add_generated_token("", 0)             # a request with max_tokens 1 is finished after prefill
+            sched.on_finish_requests(batch)
+            for r in batch.requests:
+                if not r.is_finished:
+                    pending.append((it + rng.randint(0, 14), r))
+            done = [r for due, r in pending if due <= it]
+            pending = [(due, r) for due, r in pending if due > it]
+            for r in done:
+                sched.on_request_migrated(MigratingRequest(r, [], pc))
+            steps.append(dict(arrivals=arrivals, batch=ids, migrated=[r.request_id for r in done],
+                              waiting=[len(sched.waiting_queue)] + [r.request_id for r in sched.waiting_queue[:2]],
+                              unaccepted=[r.request_id for r in sched.unaccepted_queue], on_fly=sched.num_on_fly_request_block))
+        out.append(dict(seed=seed, gpu_blocks=gpu_blocks, block_size=block_size, max_batch_size=max_bs,
+                        max_tokens_per_batch=max_tok, steps=steps))
+    return out
+
+
 def main():
     ref_root = sys.argv[1] if len(sys.argv) > 1 else str(ROOT.parent / "reference")   # a checkout beside this repo
     import_reference(ref_root)
     with tempfile.TemporaryDirectory() as tmp:
         for name, fn in (("geometry", golden_geometry), ("block_manager", golden_block_manager),
-                         ("scheduler", golden_scheduler), ("worker_calls", golden_worker_calls)):
+                         ("scheduler", golden_scheduler), ("context_scheduler", golden_context_scheduler),
+                         ("worker_calls", golden_worker_calls)):
             data = fn(tmp)
             with open(HERE / f"{name}.json", "w") as f:
                 json.dump(data, f, separators=(",", ":"))

@@ -110,3 +110,43 @@ def test_abort_and_counters():
     assert sched.get_total_num_requests() == 1
     with pytest.raises(AssertionError):
         DecodingStageFCFSScheduler(DecodingStageSchedConfig("srpt"), ParallelConfig(), bm, lambda m: None)
+
+
+def test_context_scheduler_replays_reference_decisions(golden_dir):
+    """Prefill batches while finished requests still hold their blocks, waiting to be migrated."""
+    from distserve_b200.request import BatchedRequests  # noqa: F401  (the scheduler returns these)
+    from distserve_b200.scheduler import ContextStageFCFSScheduler, ContextStageSchedConfig
+
+    with open(golden_dir / "context_scheduler.json") as f:
+        scenarios = json.load(f)
+    assert sum(1 for sc in scenarios for s in sc["steps"] if s["waiting"][0]) >= 30      # back-pressure does occur
+    for sc in scenarios:
+        rng = random.Random(sc["seed"])
+        block_size = sc["block_size"]
+        pc = ParallelConfig()
+        bm = BlockManager("context", sc["gpu_blocks"], 1, KVModelConfig(12, 12, 64), pc, CacheConfig(block_size, 256), lambda *a: None)
+        sched = ContextStageFCFSScheduler(ContextStageSchedConfig("fcfs", sc["max_batch_size"], sc["max_tokens_per_batch"]), pc, bm)
+        pending, next_id = [], 0
+        for it, ref in enumerate(sc["steps"]):
+            arrivals = []
+            for _ in range(rng.choice([0, 1, 1, 2])):
+                n = rng.randint(4, 10 * block_size)
+                sched.add_request(Request(next_id, [0] * n, max_tokens=rng.choice([1, 8])))
+                arrivals.append([next_id, n])
+                next_id += 1
+            batch = sched.get_next_batch_and_pop()
+            ids = batch.get_request_ids()
+            for r in batch.requests:
+                r.add_generated_token()
+            sched.on_finish_requests(batch)
+            for r in batch.requests:
+                if not r.is_finished:
+                    pending.append((it + rng.randint(0, 14), r))
+            done = [r for due, r in pending if due <= it]
+            pending = [(due, r) for due, r in pending if due > it]
+            for r in done:
+                sched.on_request_migrated(MigratingRequest(r, [], pc))
+            mine = dict(arrivals=arrivals, batch=ids, migrated=[r.request_id for r in done],
+                        waiting=[len(sched.waiting_queue)] + [r.request_id for r in sched.waiting_queue[:2]],
+                        unaccepted=[r.request_id for r in sched.unaccepted_queue], on_fly=sched.num_on_fly_request_block)
+            assert mine == ref, f"seed {sc['seed']} iteration {it}: {mine} != {ref}"
