@@ -42,6 +42,7 @@ SIGNATURES = {
     "kvmig_abi_version": (C.c_int, []),
     "kvmig_last_error": (C.c_char_p, []),
     "kvmig_get_ipc_mem_handle": (C.c_int, [C.c_void_p, _SHAPEP, _I64P]),
+    "kvmig_handle_is_local": (C.c_int, [_I64P, C.c_int64]),
     "kvmig_register_ipc_mem_handle": (C.c_int, [_I64P, C.c_int64, _I64P, C.c_int64, C.c_int64, C.c_int64, _I64P, _I64P]),
     "kvmig_migrate_blocks": (C.c_int, [C.c_int64, C.c_int64, _I64P, C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_int64,
                                        _I64P, C.c_int64, C.c_void_p, C.c_void_p, _SHAPEP, C.c_void_p]),
@@ -109,6 +110,14 @@ def get_ipc_mem_handle(pool_ptr: int, shape: PoolShape) -> list:
     out = (C.c_int64 * HANDLE_WORDS)()
     _check(lib().kvmig_get_ipc_mem_handle(pool_ptr, C.byref(shape), out))
     return list(out)
+
+
+def handle_is_local(handle) -> bool:
+    """Was this handle exported by the calling process (pid and per-process number both match)?"""
+    rc = lib().kvmig_handle_is_local(_i64(handle), len(handle))
+    if rc < 0:
+        raise KvmigError(rc, lib().kvmig_last_error().decode())
+    return bool(rc)
 
 
 def register_ipc_mem_handle(k_handle, v_handle, num_layers, num_heads, ctx_pc, dec_pc) -> None:

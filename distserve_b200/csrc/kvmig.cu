@@ -22,12 +22,14 @@
 #include <algorithm>
 #include <array>
 #include <atomic>
+#include <chrono>
 #include <cstdarg>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
 #include <map>
 #include <mutex>
+#include <random>
 #include <string>
 #include <tuple>
 #include <vector>
@@ -66,7 +68,7 @@ constexpr int64_t kMagic = 0x4b564d4947303031LL;  // "KVMIG001"
 enum {
     HW_MAGIC = 0, HW_IPC = 1 /*..8*/, HW_OFFSET = 9, HW_BYTES = 10, HW_PID = 11, HW_PTR = 12,
     HW_IPC_VALID = 13, HW_NB = 14, HW_NL = 15, HW_NH = 16, HW_BS = 17, HW_HD = 18, HW_ES = 19,
-    HW_DEVICE = 20, HW_RESERVED0 = 21, HW_RESERVED1 = 22, HW_CHECK = 23
+    HW_DEVICE = 20, HW_NONCE = 21, HW_RESERVED1 = 22, HW_CHECK = 23
 };
 
 int64_t handle_checksum(const int64_t* w) {
@@ -87,11 +89,35 @@ struct Options {
         dynamic_units{1}, wait_limit_ms{2000}, lose_unit_plus1{0}, unit_batch{0};
 };
 Options g_opt;
+std::atomic<uint64_t> g_option_gen{1};   // bumped by every kvmig_set_option
 
 struct Counters {
     std::atomic<int64_t> kernel_launches{0}, memcpy_calls{0}, bytes_migrated{0}, bytes_swapped{0}, mapped_peers{0};
+    // Host time of the migration entry points, by segment (nanoseconds, summed over calls): turning the arguments
+    // into launch descriptors, checking the block ids, deciding whether the launch may overlap its predecessors,
+    // filling the parameters and launching, and waiting for the kernel.
+    std::atomic<int64_t> migrate_calls{0}, plan_cache_hits{0}, ns_prepare{0}, ns_validate{0}, ns_order{0}, ns_launch{0}, ns_wait{0};
 };
 Counters g_cnt;
+
+inline int64_t now_ns() {
+    return std::chrono::duration_cast<std::chrono::nanoseconds>(std::chrono::steady_clock::now().time_since_epoch()).count();
+}
+
+// A number drawn once per process.  It travels in every exported handle next to the pid: a handle is treated
+// as "exported by this very process" only if both match, because two workers in different pid namespaces
+// (containers) can carry the same pid.
+int64_t process_nonce() {
+    static const int64_t nonce = [] {
+        std::random_device rd;
+        uint64_t v = ((uint64_t)rd() << 32) ^ (uint64_t)rd() ^ ((uint64_t)now_ns() << 1) ^ ((uint64_t)getpid() << 40);
+        v &= 0x7fffffffffffffffULL;
+        return (int64_t)(v ? v : 1);
+    }();
+    return nonce;
+}
+
+inline bool exported_by_this_process(const int64_t* w);
 
 struct CtxKey {
     int64_t tp, pp, pp_rank, tp_rank;
@@ -108,6 +134,14 @@ struct CtxEntry {
     bool mapped = false;
 };
 
+struct Range {
+    const char* p = nullptr;
+    size_t n = 0;
+    bool meets(const Range& o) const { return n && o.n && p < o.p + o.n && o.p < p + n; }
+};
+
+constexpr int kMaxReadRanges = 64;
+
 struct Slot {
     int* h_tab = nullptr;      // pinned
     int* d_tab = nullptr;
@@ -120,6 +154,42 @@ struct Slot {
     uint64_t seq = 0;          // ticket sequence currently (or last) using this slot
     bool busy = false;
     int64_t bytes = 0;
+    // What the launch in flight touches, for the ordering decision of later launches: the stream it runs on,
+    // the two pools it writes and the context pools it reads (reads_all: too many to list, assume everything).
+    cudaStream_t stream = nullptr;
+    Range writes[2];
+    Range reads[kMaxReadRanges];
+    int n_reads = 0;
+    bool reads_all = false;
+};
+
+struct Assembly {
+    std::vector<Seg> segs;             // two per contributing context worker: K pool, V pool
+    uintptr_t align_bits = 0;          // OR of every address, stride and run length
+    int64_t src_num_blocks = INT64_MAX;
+    std::vector<Range> reads;          // the context pools those segments read
+};
+
+struct LaunchShape {
+    int64_t kernel = 0;        // 1 vector loads, 2 bulk-copy pipeline
+    int vec = 16;              // widest vector every address and length allows
+    int64_t stages = 0, chunk = 0, ctas_per_sm = 0;
+    size_t smem = 0;
+};
+
+// Everything about a call that does not depend on its block lists.  A worker migrates request after request
+// with the same stage layouts, pools and options, so the result of planning is kept and reused until one of
+// them changes.
+struct Prepared {
+    bool valid = false;
+    int64_t key[10] = {};
+    kvmig_pool_shape shape = {};
+    const void* k = nullptr;
+    const void* v = nullptr;
+    uint64_t registry_gen = 0, option_gen = 0;
+    bool nothing_to_move = false;      // the layer window misses this worker
+    Assembly as;
+    LaunchShape ls;
 };
 
 struct DeviceState {
@@ -127,6 +197,7 @@ struct DeviceState {
     int sm_count = 0;
     int max_smem_optin = 0;
     std::map<CtxKey, CtxEntry> registry;
+    uint64_t registry_gen = 1;           // bumped whenever the registry changes
     std::map<std::array<int64_t, 8>, char*> ipc_bases;   // opened IPC allocations
     Slot slots[KVMIG_MAX_INFLIGHT];
     uint64_t next_seq = 1;
@@ -136,7 +207,10 @@ struct DeviceState {
     // Per destination pool (keyed by the K pool's address): ticket sequence of the last launch that wrote
     // each block, used to decide whether a new launch may overlap the launches still in flight.
     std::map<const void*, std::vector<uint64_t>> last_writer;
+    const void* marks_pool = nullptr;            // the pool looked up last, and its marks
+    std::vector<uint64_t>* marks = nullptr;
     std::vector<char> seen;   // duplicate-target bitmap, all zero between calls
+    Prepared prepared;        // planning result of the previous ticketed call
 };
 
 std::mutex g_mu;
@@ -191,9 +265,13 @@ int validate_handle(const int64_t* w, int64_t len, const char* what) {
     return 0;
 }
 
+inline bool exported_by_this_process(const int64_t* w) {
+    return w[HW_PID] == (int64_t)getpid() && w[HW_NONCE] == process_nonce();
+}
+
 // Resolve an exported pool to an address usable on the current device.
 int map_pool(DeviceState& st, int dev, const int64_t* w, char** out) {
-    if (w[HW_PID] == (int64_t)getpid()) {
+    if (exported_by_this_process(w)) {
         // Exported by this very process: CUDA IPC cannot open its own handles.
         char* p = reinterpret_cast<char*>((uintptr_t)w[HW_PTR]);
         cudaPointerAttributes attr;
@@ -351,11 +429,6 @@ void clip_to_layers(std::vector<SegPlan>* plan, int64_t first_layer, int64_t lay
     plan->swap(clipped);
 }
 
-struct Assembly {
-    std::vector<Seg> segs;             // two per contributing context worker: K pool, V pool
-    uintptr_t align_bits = 0;          // OR of every address, stride and run length
-    int64_t src_num_blocks = INT64_MAX;
-};
 
 // Turn the planned overlaps into strided-copy descriptors over the registered (mapped) context pools.
 // With map_missing a registered-but-unmapped pool is mapped now; without, that is an error (mapping
@@ -393,6 +466,8 @@ int assemble_segments(DeviceState& st, int dev, const std::vector<SegPlan>& plan
             ce.mapped = true;
         }
         out->src_num_blocks = std::min(out->src_num_blocks, std::min(ce.hk[HW_NB], ce.hv[HW_NB]));
+        out->reads.push_back(Range{ce.k, (size_t)ce.hk[HW_BYTES]});
+        out->reads.push_back(Range{ce.v, (size_t)ce.hv[HW_BYTES]});
         for (int x = 0; x < 2; ++x) {
             Seg g;
             const char* sbase = x == 0 ? ce.k : ce.v;
@@ -442,12 +517,6 @@ int validate_ids(DeviceState& st, const int64_t* ctx_blocks, const int64_t* dec_
     return rc;
 }
 
-struct LaunchShape {
-    int64_t kernel = 0;        // 1 vector loads, 2 bulk-copy pipeline
-    int vec = 16;              // widest vector every address and length allows
-    int64_t stages = 0, chunk = 0, ctas_per_sm = 0;
-    size_t smem = 0;
-};
 
 // Kernel, ring geometry and CTAs per SM from the options and the alignment of this call.
 int shape_launch(DeviceState& st, uintptr_t align_bits, LaunchShape* ls) {
@@ -461,7 +530,7 @@ int shape_launch(DeviceState& st, uintptr_t align_bits, LaunchShape* ls) {
     if (ls->chunk < 16 || ls->chunk % 16) return fail(KVMIG_EINVAL, "chunk_bytes must be a positive multiple of 16");
     ls->ctas_per_sm = g_opt.ctas_per_sm.load();
     if (ls->kernel == 2) {
-        ls->smem = (size_t)ls->stages * ls->chunk + (size_t)ls->stages * (8 + 8 + 4) + 16;
+        ls->smem = (size_t)ls->stages * ls->chunk + (size_t)ls->stages * (8 + 8 + 4 + 4) + 16;
         if ((int64_t)ls->smem > st.max_smem_optin)
             return fail(KVMIG_ELIMIT, "stages x chunk_bytes = %zu B exceeds the %d B of shared memory a CTA may use", ls->smem,
                         st.max_smem_optin);
@@ -565,10 +634,21 @@ cudaError_t launch_device_tables(const MigParams& p, unsigned grid, const Launch
 
 // ---- the ticketed entry point (awaited and asynchronous calls, optional layer window) ----------
 
+// Is the launch that occupies `sl` still executing?  `cache` holds one answer per slot for the current call
+// (-1 not asked yet), so that a slot's event is queried at most once.
+bool slot_running(DeviceState& st, int si, int* cache) {
+    if (cache[si] < 0) {
+        cache[si] = cudaEventQuery(st.slots[si].done) == cudaSuccess ? 0 : 1;
+        (void)cudaGetLastError();   // "not ready" is reported through the error state
+    }
+    return cache[si] == 1;
+}
+
 int enqueue_migration(int64_t ctx_pp, int64_t ctx_tp, const int64_t* ctx_blocks, int64_t n_ctx, int64_t dec_pp,
                       int64_t dec_tp, int64_t dec_pp_rank, int64_t dec_tp_rank, const int64_t* dec_blocks, int64_t n_dec,
                       void* k_cache, void* v_cache, const kvmig_pool_shape* shape, cudaStream_t stream, uint64_t* ticket,
                       int64_t layer_begin = 0, int64_t layer_end = INT64_MAX) {
+    const int64_t t_begin = now_ns();
     g_err.clear();
     if (ticket) *ticket = 0;
     int rc = check_lists("migrate_blocks", shape, ctx_blocks, n_ctx, dec_blocks, n_dec, k_cache, v_cache);
@@ -580,26 +660,53 @@ int enqueue_migration(int64_t ctx_pp, int64_t ctx_tp, const int64_t* ctx_blocks,
     rc = ensure_device(&stp, &dev);
     if (rc) return rc;
     DeviceState& st = *stp;
+    g_cnt.migrate_calls++;
 
-    const int64_t L = shape->num_layers * dec_pp, H = shape->num_heads * dec_tp;
-    std::vector<SegPlan> plan;
-    rc = plan_segments(L, H, ctx_tp, ctx_pp, dec_tp, dec_tp_rank, dec_pp, dec_pp_rank, &plan);
-    if (rc) return rc;
-    if (layer_begin < 0 || layer_end < layer_begin)
-        return fail(KVMIG_EINVAL, "layer window [%lld, %lld) is not a range", (long long)layer_begin, (long long)layer_end);
-    layer_end = std::min(layer_end, L);
-    if (layer_begin > 0 || layer_end < L) clip_to_layers(&plan, dec_pp_rank * shape->num_layers, layer_begin, layer_end);
+    // Planning, segment assembly and kernel geometry depend only on the layouts, the pools, the registry and the
+    // options: reuse the previous call's when none of them changed.
+    Prepared& pr = st.prepared;
+    const int64_t key[10] = {ctx_pp, ctx_tp, dec_pp, dec_tp, dec_pp_rank, dec_tp_rank, layer_begin, layer_end, 0, 0};
+    const uint64_t option_gen = g_option_gen.load();
+    if (pr.valid && std::memcmp(pr.key, key, sizeof key) == 0 && std::memcmp(&pr.shape, shape, sizeof *shape) == 0 &&
+        pr.k == k_cache && pr.v == v_cache && pr.registry_gen == st.registry_gen && pr.option_gen == option_gen) {
+        g_cnt.plan_cache_hits++;
+    } else {
+        pr.valid = false;
+        const int64_t L = shape->num_layers * dec_pp, H = shape->num_heads * dec_tp;
+        std::vector<SegPlan> plan;
+        rc = plan_segments(L, H, ctx_tp, ctx_pp, dec_tp, dec_tp_rank, dec_pp, dec_pp_rank, &plan);
+        if (rc) return rc;
+        if (layer_begin < 0 || layer_end < layer_begin)
+            return fail(KVMIG_EINVAL, "layer window [%lld, %lld) is not a range", (long long)layer_begin, (long long)layer_end);
+        const int64_t window_end = std::min(layer_end, L);
+        if (layer_begin > 0 || window_end < L) clip_to_layers(&plan, dec_pp_rank * shape->num_layers, layer_begin, window_end);
+        pr.as = Assembly();
+        rc = assemble_segments(st, dev, plan, L, H, ctx_tp, ctx_pp, shape, k_cache, v_cache, /*map_missing=*/true, &pr.as);
+        if (rc) return rc;
+        pr.nothing_to_move = plan.empty();
+        pr.ls = LaunchShape();
+        if (!pr.nothing_to_move) {
+            rc = shape_launch(st, pr.as.align_bits, &pr.ls);
+            if (rc) return rc;
+        }
+        std::memcpy(pr.key, key, sizeof key);
+        pr.shape = *shape;
+        pr.k = k_cache;
+        pr.v = v_cache;
+        pr.registry_gen = st.registry_gen;
+        pr.option_gen = option_gen;
+        pr.valid = true;
+    }
+    const Assembly& as = pr.as;
+    const LaunchShape& ls = pr.ls;
+    const int64_t t_prepared = now_ns();
+    g_cnt.ns_prepare += t_prepared - t_begin;
 
-    Assembly as;
-    rc = assemble_segments(st, dev, plan, L, H, ctx_tp, ctx_pp, shape, k_cache, v_cache, /*map_missing=*/true, &as);
-    if (rc) return rc;
     rc = validate_ids(st, ctx_blocks, dec_blocks, n_ctx, as.src_num_blocks, shape->num_blocks);
+    const int64_t t_validated = now_ns();
+    g_cnt.ns_validate += t_validated - t_prepared;
     if (rc) return rc;
-    if (n_ctx == 0 || plan.empty()) return 0;   // nothing to move (empty lists, or the window misses this worker)
-
-    LaunchShape ls;
-    rc = shape_launch(st, as.align_bits, &ls);
-    if (rc) return rc;
+    if (n_ctx == 0 || pr.nothing_to_move) return 0;   // nothing to move (empty lists, or the window misses this worker)
 
     // Ticket slot.
     uint64_t seq = st.next_seq++;
@@ -611,28 +718,96 @@ int enqueue_migration(int64_t ctx_pp, int64_t ctx_tp, const int64_t* ctx_blocks,
     rc = grow_slot(sl, inline_tables ? 0 : n_ctx);
     if (rc) return rc;
     sl.status[0] = sl.status[1] = sl.status[2] = sl.status[3] = 0;
-    // May this launch overlap the migrations still in flight?  Only if it writes none of their blocks.
+
+    // ---- ordering against the migrations still in flight ------------------------------------------------
+    // A launch may begin before earlier ones have finished (programmatic dependent launch) only if it is
+    // independent of every one of them that is still executing:
+    //   * it reads no pool that one of them writes and writes no pool that one of them reads;
+    //   * where it writes a pool one of them writes, it writes other blocks, or other layers of the same blocks.
+    // Otherwise the grid waits for its predecessor in the stream before it touches memory (grids complete in
+    // stream order, so that covers every earlier launch on the stream), and a conflicting launch on another
+    // stream is waited for through its event.
+    const int64_t window_end = std::min<int64_t>(layer_end, shape->num_layers * dec_pp);
     const bool overlap = inline_tables && g_opt.overlap_launches.load() != 0;
     bool depends = !overlap;
+    bool cross_stream_wait = false;
+    int running[KVMIG_MAX_INFLIGHT];
+    for (int& r : running) r = -1;
+    const Range my_writes[2] = {Range{static_cast<const char*>(k_cache), (size_t)(shape->num_blocks * block_bytes(*shape))},
+                                Range{static_cast<const char*>(v_cache), (size_t)(shape->num_blocks * block_bytes(*shape))}};
+    auto must_follow = [&](int si) -> int {
+        // The launch in slot si conflicts with this one: order this one after it.
+        Slot& other = st.slots[si];
+        if (!slot_running(st, si, running)) return 0;
+        depends = true;
+        if (other.stream != stream) {
+            CU_TRY(cudaStreamWaitEvent(stream, other.done, 0));
+            cross_stream_wait = true;
+        }
+        return 0;
+    };
+    bool newest_known = false, other_streams = false;
+    uint64_t newest_seq = 0;
+    int newest_slot = -1;
+    for (int si = 0; si < KVMIG_MAX_INFLIGHT; ++si) {
+        Slot& other = st.slots[si];
+        if (!other.busy || &other == &sl) continue;
+        if (other.stream != stream) other_streams = true;
+        if (other.stream == stream && other.seq > newest_seq) { newest_seq = other.seq; newest_slot = si; newest_known = true; }
+        bool conflict = false;
+        for (int x = 0; x < 2 && !conflict; ++x) {
+            // same destination pools: decided per block and layer window below
+            if (other.writes[x].p == my_writes[x].p && other.writes[x].n == my_writes[x].n) continue;
+            for (int y = 0; y < 2 && !conflict; ++y) conflict = other.writes[x].meets(my_writes[y]);
+        }
+        if (!conflict && other.reads_all) conflict = true;
+        for (int r = 0; r < other.n_reads && !conflict; ++r)
+            conflict = other.reads[r].meets(my_writes[0]) || other.reads[r].meets(my_writes[1]);
+        for (size_t r = 0; r < as.reads.size() && !conflict; ++r)
+            conflict = as.reads[r].meets(other.writes[0]) || as.reads[r].meets(other.writes[1]);
+        if (conflict && (rc = must_follow(si))) return rc;
+    }
     {
-        std::vector<uint64_t>& marks = st.last_writer[k_cache];
+        if (st.marks_pool != k_cache || !st.marks) {
+            st.marks = &st.last_writer[k_cache];
+            st.marks_pool = k_cache;
+        }
+        std::vector<uint64_t>& marks = *st.marks;
         if ((int64_t)marks.size() < shape->num_blocks) marks.resize((size_t)shape->num_blocks, 0);
-        int running[KVMIG_MAX_INFLIGHT];   // -1 unknown, 0 finished, 1 still running; one query per slot at most
-        for (int& r : running) r = -1;
+        bool hidden_writers = false;   // a block's mark names a launch on other layers: an older writer may hide behind it
         for (int64_t i = 0; i < n_ctx; ++i) {
             uint64_t& m = marks[(size_t)dec_blocks[i]];
-            if (m != 0 && !depends) {
+            if (m != 0 && (!depends || other_streams)) {
                 const int si = (int)(m % KVMIG_MAX_INFLIGHT);
                 Slot& other = st.slots[si];
-                if (other.seq == m && other.busy && other.layer0 < layer_end && layer_begin < other.layer1) {
-                    if (running[si] < 0) running[si] = cudaEventQuery(other.done) == cudaSuccess ? 0 : 1;
-                    if (running[si] == 1) depends = true;
+                if (other.seq == m && other.busy) {
+                    if (other.layer0 < window_end && layer_begin < other.layer1) {
+                        if ((rc = must_follow(si))) return rc;
+                    } else {
+                        hidden_writers = true;
+                    }
                 }
             }
             m = seq;
         }
-        (void)cudaGetLastError();   // cudaEventQuery reports "not ready" through the error state
+        if (hidden_writers && (!depends || other_streams)) {
+            // Marks keep one launch per block.  Behind a launch on other layers there may be an older one on
+            // these layers that is still running: look at every launch into this pool whose window meets ours.
+            for (int si = 0; si < KVMIG_MAX_INFLIGHT; ++si) {
+                Slot& other = st.slots[si];
+                if (!other.busy || &other == &sl || other.writes[0].p != my_writes[0].p) continue;
+                if (other.layer0 < window_end && layer_begin < other.layer1 && (rc = must_follow(si))) return rc;
+            }
+        }
     }
+    // Starting early is only meaningful behind a migration of this library that is still executing.  Behind
+    // anything else (a producer that filled the source pool, a decode step) the grid waits for its predecessor
+    // before it touches memory, which is what makes that kernel's writes visible to it.
+    if (!depends && (!newest_known || !slot_running(st, newest_slot, running))) depends = true;
+    const bool launch_overlapped = overlap && !cross_stream_wait;
+    const int64_t t_ordered = now_ns();
+    g_cnt.ns_order += t_ordered - t_validated;
+
     if (!inline_tables) {
         for (int64_t i = 0; i < n_ctx; ++i) {
             sl.h_tab[i] = (int)ctx_blocks[i];
@@ -671,8 +846,8 @@ int enqueue_migration(int64_t ctx_pp, int64_t ctx_tp, const int64_t* ctx_blocks,
             cudaError_t e;
             if (inline_tables)
                 e = nb <= kInlineSmall
-                        ? launch_bulk_inline<kInlineSmall>(p, ctx_blocks + b0, dec_blocks + b0, grid, ls, stream, overlap)
-                        : launch_bulk_inline<kInlineLarge>(p, ctx_blocks + b0, dec_blocks + b0, grid, ls, stream, overlap);
+                        ? launch_bulk_inline<kInlineSmall>(p, ctx_blocks + b0, dec_blocks + b0, grid, ls, stream, launch_overlapped)
+                        : launch_bulk_inline<kInlineLarge>(p, ctx_blocks + b0, dec_blocks + b0, grid, ls, stream, launch_overlapped);
             else
                 e = launch_device_tables(p, grid, ls, stream);
             if (e != cudaSuccess) return fail(KVMIG_ECUDA, "launching the migration kernel: %s", cudaGetErrorString(e));
@@ -683,9 +858,16 @@ int enqueue_migration(int64_t ctx_pp, int64_t ctx_tp, const int64_t* ctx_blocks,
     sl.busy = true;
     sl.seq = seq;
     sl.layer0 = layer_begin;
-    sl.layer1 = layer_end;
+    sl.layer1 = window_end;
     sl.bytes = bytes_per_block * n_ctx;
+    sl.stream = stream;
+    sl.writes[0] = my_writes[0];
+    sl.writes[1] = my_writes[1];
+    sl.reads_all = as.reads.size() > (size_t)kMaxReadRanges;
+    sl.n_reads = sl.reads_all ? 0 : (int)as.reads.size();
+    for (int r = 0; r < sl.n_reads; ++r) sl.reads[r] = as.reads[r];
     if (ticket) *ticket = ((uint64_t)(unsigned)dev << 48) | seq;
+    g_cnt.ns_launch += now_ns() - t_ordered;
     return 0;
 }
 
@@ -706,7 +888,9 @@ int wait_ticket(uint64_t ticket) {
         // stays valid (events are created once per slot and never destroyed).
         cudaEvent_t done = sl.done;
         lock.unlock();
+        const int64_t t0 = now_ns();
         cudaError_t e = cudaEventSynchronize(done);
+        g_cnt.ns_wait += now_ns() - t0;
         lock.lock();
         if (e != cudaSuccess) rc = fail(KVMIG_ECUDA, "waiting for the migration kernel: %s", cudaGetErrorString(e));
         if (!rc && sl.seq == seq) rc = retire_slot(st, sl);   // returns at once: the event has completed
@@ -882,12 +1066,20 @@ int kvmig_get_ipc_mem_handle(const void* pool, const kvmig_pool_shape* shape, in
     w[HW_OFFSET] = offset;
     w[HW_BYTES] = bytes;
     w[HW_PID] = (int64_t)getpid();
+    w[HW_NONCE] = process_nonce();
     w[HW_PTR] = (int64_t)(uintptr_t)pool;
     w[HW_NB] = shape->num_blocks; w[HW_NL] = shape->num_layers; w[HW_NH] = shape->num_heads;
     w[HW_BS] = shape->block_size; w[HW_HD] = shape->head_dim; w[HW_ES] = shape->elem_size;
     w[HW_DEVICE] = attr.device;
     w[HW_CHECK] = handle_checksum(w);
     return 0;
+}
+
+int kvmig_handle_is_local(const int64_t* handle, int64_t len) {
+    g_err.clear();
+    int rc = validate_handle(handle, len, "pool");
+    if (rc) return rc;
+    return exported_by_this_process(handle) ? 1 : 0;
 }
 
 int kvmig_register_ipc_mem_handle(const int64_t* k_handle, int64_t k_len, const int64_t* v_handle, int64_t v_len,
@@ -944,6 +1136,7 @@ int kvmig_register_ipc_mem_handle(const int64_t* k_handle, int64_t k_len, const 
         ce.mapped = true;
     }
     stp->registry[key] = ce;
+    stp->registry_gen++;
     return 0;
 }
 
@@ -1051,6 +1244,7 @@ int kvmig_set_option(const char* name, int64_t value) {
     if (s == &g_opt.chunk_bytes && (value < 16 || value % 16 || value > (1 << 20)))
         return fail(KVMIG_EINVAL, "chunk_bytes must be a multiple of 16 in [16, 1 MiB]");
     s->store(value);
+    g_option_gen++;
     return 0;
 }
 
@@ -1066,6 +1260,13 @@ int64_t kvmig_get_counter(const char* name) {
     if (!std::strcmp(name, "bytes_migrated")) return g_cnt.bytes_migrated.load();
     if (!std::strcmp(name, "bytes_swapped")) return g_cnt.bytes_swapped.load();
     if (!std::strcmp(name, "mapped_peers")) return g_cnt.mapped_peers.load();
+    if (!std::strcmp(name, "migrate_calls")) return g_cnt.migrate_calls.load();
+    if (!std::strcmp(name, "plan_cache_hits")) return g_cnt.plan_cache_hits.load();
+    if (!std::strcmp(name, "ns_prepare")) return g_cnt.ns_prepare.load();
+    if (!std::strcmp(name, "ns_validate")) return g_cnt.ns_validate.load();
+    if (!std::strcmp(name, "ns_order")) return g_cnt.ns_order.load();
+    if (!std::strcmp(name, "ns_launch")) return g_cnt.ns_launch.load();
+    if (!std::strcmp(name, "ns_wait")) return g_cnt.ns_wait.load();
     return -1;
 }
 
@@ -1076,6 +1277,7 @@ int kvmig_reset_registry(void) {
     int rc = ensure_device(&st, nullptr);
     if (rc) return rc;
     st->registry.clear();
+    st->registry_gen++;
     return 0;
 }
 

@@ -179,7 +179,7 @@ __device__ __forceinline__ void fence_async_proxy() { asm volatile("fence.proxy.
 
 constexpr int kMaxStages = 16;
 
-// Shared memory: [stages * stage_bytes ring][stages mbarriers][stages dst ptr][stages sizes]
+// Shared memory: [stages * stage_bytes ring][stages mbarriers][stages dst ptr][stages sizes][stages unit numbers]
 __device__ __forceinline__ void bulk_pipeline(const MigParams& p, const int* src_ids, const int* dst_ids,
                                               unsigned int stages, unsigned int stage_bytes) {
     extern __shared__ __align__(128) unsigned char smem[];
@@ -188,6 +188,7 @@ __device__ __forceinline__ void bulk_pipeline(const MigParams& p, const int* src
     unsigned long long* bars = reinterpret_cast<unsigned long long*>(smem + (size_t)stages * stage_bytes);
     char** dst_of = reinterpret_cast<char**>(bars + stages);
     unsigned int* bytes_of = reinterpret_cast<unsigned int*>(dst_of + stages);
+    unsigned int* unit_of = bytes_of + stages;
 
     // Let the next migration grid of the stream start while this one is still running (its ramp-up
     // then hides this grid's tail).  The host sets wait_prior when the two grids are not independent.
@@ -228,6 +229,7 @@ __device__ __forceinline__ void bulk_pipeline(const MigParams& p, const int* src
         Unit w = decode_unit(p, src_ids, dst_ids, u);
         dst_of[s] = w.dst;
         bytes_of[s] = w.bytes;
+        unit_of[s] = u;
         mbar_expect_tx(&bars[s], w.bytes);
         if (p.lose_unit_plus1 && u + 1u == p.lose_unit_plus1) {
             // Failure-path exercise: the barrier is armed but the load is never issued, so the wait below
@@ -248,7 +250,7 @@ __device__ __forceinline__ void bulk_pipeline(const MigParams& p, const int* src
         const unsigned int s = k % stages;
         if (!mbar_wait_bounded(&bars[s], (k / stages) & 1u, p.wait_limit_ns)) {
             p.status[0] = kDevLoadTimeout;
-            p.status[1] = (int)k;
+            p.status[1] = (int)unit_of[s];   // the work unit (launch-wide number) whose load never signalled
             ok = false;
             break;
         }

@@ -12,6 +12,8 @@
 #include <ATen/core/Tensor.h>
 #include <c10/cuda/CUDAGuard.h>
 #include <c10/cuda/CUDAStream.h>
+#include <c10/cuda/CUDAFunctions.h>
+#include <c10/util/ArrayRef.h>
 
 #include <vector>
 
@@ -44,7 +46,7 @@ void check_pair(const at::Tensor& k, const at::Tensor& v, const char* kn, const 
 }
 
 // block_migration_ops::get_ipc_mem_handle(Tensor) -> int[]     (distserve/worker.py:133-134)
-std::vector<int64_t> get_ipc_mem_handle(at::Tensor pool) {
+std::vector<int64_t> get_ipc_mem_handle(const at::Tensor& pool) {
     TORCH_CHECK(pool.is_cuda(), "get_ipc_mem_handle: the pool must be a CUDA tensor");
     kvmig_pool_shape s = pool_shape(pool, "pool");
     c10::cuda::CUDAGuard guard(pool.device());
@@ -54,9 +56,9 @@ std::vector<int64_t> get_ipc_mem_handle(at::Tensor pool) {
 }
 
 // block_migration_ops::register_ipc_mem_handle(...)            (distserve/worker.py:239-246)
-bool register_ipc_mem_handle(std::vector<int64_t> k_handle, std::vector<int64_t> v_handle, int64_t num_layers,
-                             int64_t num_heads, std::vector<int64_t> context_parallel_config,
-                             std::vector<int64_t> decoding_parallel_config) {
+bool register_ipc_mem_handle(c10::IntArrayRef k_handle, c10::IntArrayRef v_handle, int64_t num_layers,
+                             int64_t num_heads, c10::IntArrayRef context_parallel_config,
+                             c10::IntArrayRef decoding_parallel_config) {
     TORCH_CHECK(context_parallel_config.size() == 4 && decoding_parallel_config.size() == 4,
                 "register_ipc_mem_handle: parallel configs must be [tp_size, tp_rank, pp_size, pp_rank]");
     check(kvmig_register_ipc_mem_handle(k_handle.data(), static_cast<int64_t>(k_handle.size()), v_handle.data(),
@@ -67,15 +69,18 @@ bool register_ipc_mem_handle(std::vector<int64_t> k_handle, std::vector<int64_t>
 }
 
 // block_migration_ops::migrate_blocks(...)                     (distserve/worker.py:256-267)
-void migrate_blocks(int64_t context_pp_size, int64_t context_tp_size, std::vector<int64_t> context_block_indexes,
+// The block lists are views of the caller's arguments (no copy); the tensors are taken by reference.
+void migrate_blocks(int64_t context_pp_size, int64_t context_tp_size, c10::IntArrayRef context_block_indexes,
                     int64_t decoding_pp_size, int64_t decoding_tp_size, int64_t decoding_pp_rank,
-                    int64_t decoding_tp_rank, std::vector<int64_t> decoding_block_indexes, at::Tensor k_cache,
-                    at::Tensor v_cache) {
+                    int64_t decoding_tp_rank, c10::IntArrayRef decoding_block_indexes, const at::Tensor& k_cache,
+                    const at::Tensor& v_cache) {
     TORCH_CHECK(k_cache.is_cuda() && v_cache.is_cuda(), "migrate_blocks: k_cache and v_cache must be CUDA tensors");
     check_pair(k_cache, v_cache, "k_cache", "v_cache");
     kvmig_pool_shape s = pool_shape(k_cache, "k_cache");
-    (void)pool_shape(v_cache, "v_cache");
-    c10::cuda::CUDAGuard guard(k_cache.device());
+    TORCH_CHECK(v_cache.is_contiguous(), "v_cache must be contiguous");
+    // Switch devices only when the pool is not on the current one (a worker process owns one GPU).
+    c10::cuda::OptionalCUDAGuard guard;
+    if (c10::cuda::current_device() != k_cache.device().index()) guard.set_device(k_cache.device());
     cudaStream_t stream = c10::cuda::getCurrentCUDAStream(k_cache.device().index()).stream();
     check(kvmig_migrate_blocks(context_pp_size, context_tp_size, context_block_indexes.data(),
                                static_cast<int64_t>(context_block_indexes.size()), decoding_pp_size, decoding_tp_size,
@@ -86,8 +91,8 @@ void migrate_blocks(int64_t context_pp_size, int64_t context_tp_size, std::vecto
 }
 
 // swapping_ops::swap(...)                                      (distserve/worker.py:303-311)
-void swap(std::vector<int64_t> source_block_ids, std::vector<int64_t> target_block_ids, bool is_swap_in,
-          at::Tensor k_cache, at::Tensor v_cache, at::Tensor k_swap, at::Tensor v_swap) {
+void swap(c10::IntArrayRef source_block_ids, c10::IntArrayRef target_block_ids, bool is_swap_in,
+          const at::Tensor& k_cache, const at::Tensor& v_cache, const at::Tensor& k_swap, const at::Tensor& v_swap) {
     TORCH_CHECK(k_cache.is_cuda() && v_cache.is_cuda(), "swap: k_cache and v_cache must be CUDA tensors");
     TORCH_CHECK(k_swap.is_cpu() && v_swap.is_cpu(), "swap: k_swap and v_swap must be host tensors");
     check_pair(k_cache, v_cache, "k_cache", "v_cache");

@@ -74,6 +74,7 @@ class KVWorker:
         self._swaps_issued = {True: 0, False: 0}        # per direction (is_swap_in)
         self._swaps_known_done = {True: 0, False: 0}    # highest mark known to have completed
         self.blocked_swapping_time = 0.0
+        self._bind_migrate_op()
 
     # --- pools and handles ---------------------------------------------------------------
     def kv_cache_shape(self, num_blocks: int) -> Tuple[int, int, int, int, int]:
@@ -109,17 +110,25 @@ class KVWorker:
             torch.cuda.synchronize(self.device)
 
     # --- migration -----------------------------------------------------------------------
+    def _bind_migrate_op(self):
+        """Resolve, once, the operator object and this worker's own layout in the operator's argument order
+        (the lookup through ``torch.ops`` and the overload choice are host time on every request otherwise)."""
+        packet = torch.ops.block_migration_ops.migrate_blocks
+        self._migrate_op = getattr(packet, "default", packet)
+        pc = self.parallel_config
+        self._own_layout = (pc.pipeline_parallel_size, pc.tensor_parallel_size, pc.pipeline_parallel_rank,
+                            pc.tensor_parallel_rank)
+        return self._migrate_op
+
     def migrate_blocks(self, context_block_indexes: List[int], context_parallel_config: ParallelConfig,
                        decoding_block_indexes: List[int]) -> None:
         """Pull the listed context-stage blocks into this worker's pools
-        (distserve/worker.py:250-267).  Returns when the sources have been read."""
-        with torch.cuda.device(self.device):
-            torch.ops.block_migration_ops.migrate_blocks(
-                context_parallel_config.pipeline_parallel_size, context_parallel_config.tensor_parallel_size,
-                context_block_indexes,
-                self.parallel_config.pipeline_parallel_size, self.parallel_config.tensor_parallel_size,
-                self.parallel_config.pipeline_parallel_rank, self.parallel_config.tensor_parallel_rank,
-                decoding_block_indexes, self.k_cache, self.v_cache)
+        (distserve/worker.py:250-267).  Returns when the sources have been read.  The operator itself
+        makes the pools' device current for the call and launches on that device's current stream."""
+        op = getattr(self, "_migrate_op", None) or self._bind_migrate_op()
+        pp, tp, pp_rank, tp_rank = self._own_layout
+        op(context_parallel_config.pipeline_parallel_size, context_parallel_config.tensor_parallel_size,
+           context_block_indexes, pp, tp, pp_rank, tp_rank, decoding_block_indexes, self.k_cache, self.v_cache)
 
     def _pool_shape(self) -> capi.PoolShape:
         return capi.PoolShape.of(*self.k_cache.shape, self.k_cache.element_size())

@@ -68,10 +68,22 @@ KVMIG_API const char* kvmig_last_error(void);
  * (distserve/worker.py:133-134).  `pool` is the device address of element 0;
  * `handle_out` receives KVMIG_HANDLE_WORDS words: the CUDA IPC handle of the
  * enclosing allocation, the pool's byte offset inside it, its shape, and the
- * exporter's pid (a handle registered by the process that exported it is
- * resolved without CUDA IPC, which cannot open its own handles).
+ * exporter's pid together with a number the exporting process drew at random
+ * when it started (a handle registered by the process that exported it is
+ * resolved without CUDA IPC, which cannot open its own handles; the pid alone
+ * would not identify that process, because workers in different pid
+ * namespaces can carry the same pid).
  */
 KVMIG_API int kvmig_get_ipc_mem_handle(const void* pool, const kvmig_pool_shape* shape, int64_t* handle_out);
+
+/*
+ * 1 if `handle` was exported by the calling process (pid and per-process
+ * number both match), 0 if it came from another process, a negative KVMIG_E*
+ * code if the words are not a valid handle.  Needs no device.  (No
+ * counterpart in the reference; it tells a host which of the two mapping
+ * routes registration will take.)
+ */
+KVMIG_API int kvmig_handle_is_local(const int64_t* handle, int64_t handle_len);
 
 /*
  * Make one context-stage worker's K and V pools addressable from the calling
@@ -123,6 +135,21 @@ KVMIG_API int kvmig_migrate_blocks(int64_t ctx_pp_size, int64_t ctx_tp_size,
  * (the call cadence of distserve/decoding_stage_scheduler.py:247-260 is one
  * awaited request at a time).  At most KVMIG_MAX_INFLIGHT tickets may be
  * outstanding per device; older ones are awaited implicitly.
+ *
+ * Ordering.  Migrations enqueued on one stream complete in the order they were
+ * enqueued, and whatever the caller enqueues on that stream afterwards runs
+ * after all of them.  A migration may *begin* before earlier ones have
+ * finished, but only when it is independent of every one of them that is still
+ * executing: it reads no pool that one of them writes, writes no pool that one
+ * of them reads, and where both write the same pools it writes other blocks
+ * (or, for kvmig_migrate_layers_async, other layers of the same blocks).  A
+ * migration that conflicts with one still executing on ANOTHER stream is
+ * ordered after it through that migration's event.  Work of other libraries is
+ * ordered by its own completion: a kernel that the caller puts on the stream
+ * between two migrations runs after the first has finished, and the second
+ * begins after that kernel has finished.  Ordering against work on other
+ * streams that is not a migration of this library is the caller's business,
+ * as with any stream.
  */
 #define KVMIG_MAX_INFLIGHT 8
 KVMIG_API int kvmig_migrate_blocks_async(int64_t ctx_pp_size, int64_t ctx_tp_size,
@@ -168,12 +195,18 @@ KVMIG_API int kvmig_migrate_layers_async(int64_t ctx_pp_size, int64_t ctx_tp_siz
  * completion rule (it returns when the source blocks have been read), but its
  * scratch is a fixed array compiled into the library (33 KiB of device memory
  * on every GPU that loads it, held until the process exits), and it calls no
- * cudaMalloc, cudaFree, cudaHostAlloc, event creation or other allocating
- * routine.
+ * cudaMalloc, cudaFree, cudaHostAlloc, event creation or other routine that
+ * allocates device or pinned memory.  (Ordinary host-heap use remains: the
+ * planning step builds a few small vectors per call.)  Every call ends by
+ * waiting for its stream.
  *
  * Limits and rules:
  *  - at most KVMIG_STATIC_MAX_BLOCKS block indexes per call; more is refused
  *    with KVMIG_ELIMIT (split the lists, or use kvmig_migrate_blocks);
+ *  - at most 8 context workers may contribute to the calling worker's
+ *    rectangle (one launch carries 16 strided-copy descriptors, two per
+ *    contributing worker); a reshard that needs more is refused with
+ *    KVMIG_ELIMIT;
  *  - every context worker it reads must already have been mapped by
  *    kvmig_register_ipc_mem_handle for this decoding rank (mapping a peer pool
  *    is registration's job; this call refuses instead of mapping);
@@ -240,7 +273,14 @@ KVMIG_API int kvmig_swap(const int64_t* source_block_ids, int64_t num_source,
  *             arms its completion barrier but never issues its load, so that
  *             wait runs out (default 0)
  *   counters: "kernel_launches", "memcpy_calls", "bytes_migrated",
- *             "bytes_swapped", "mapped_peers"
+ *             "bytes_swapped", "mapped_peers", "migrate_calls",
+ *             "plan_cache_hits" (calls that reused the previous call's
+ *             planning), and the host time of the migration entry points by
+ *             segment, in nanoseconds summed over calls: "ns_prepare"
+ *             (arguments to launch descriptors), "ns_validate" (block ids),
+ *             "ns_order" (may the launch overlap its predecessors?),
+ *             "ns_launch" (parameters, launch, event), "ns_wait" (waiting for
+ *             the kernel in kvmig_migrate_wait / kvmig_migrate_blocks)
  */
 KVMIG_API int kvmig_set_option(const char* name, int64_t value);
 KVMIG_API int64_t kvmig_get_option(const char* name);

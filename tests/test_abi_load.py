@@ -65,6 +65,69 @@ def test_validation_happens_before_cuda(built_libs):
     assert capi.get_option("chunk_bytes") % 16 == 0
 
 
+def _handle_checksum(words):
+    """The handle's last word: a hash over the 23 words before it (kvmig.cu: handle_checksum)."""
+    mask = (1 << 64) - 1
+    h = 0x9E3779B97F4A7C15
+    for w in words[:23]:
+        h ^= ((w & mask) + 0x9E3779B97F4A7C15 + ((h << 6) & mask) + (h >> 2)) & mask
+    return h - (1 << 64) if h >= (1 << 63) else h
+
+
+def test_a_handle_with_this_pid_but_another_process_number_is_not_local(built_libs):
+    """Two workers in different pid namespaces can carry the same pid, so the pid alone must not make a
+    handle "exported by this process" (such a handle's raw address is dereferenced): the per-process number
+    drawn at start-up has to match as well.  Forged here without a device: well-formed words, this pid, a
+    different number."""
+    from distserve_b200 import capi
+
+    magic = 0x4B564D4947303031
+    words = [0] * capi.HANDLE_WORDS
+    words[0] = magic
+    words[10] = 8 * 2 * 2 * 4 * 8 * 2                     # pool bytes for the shape below
+    words[11] = os.getpid()
+    words[12] = 0x7F0000000000                            # "address" in the forging process
+    words[14:20] = [8, 2, 2, 4, 8, 2]
+    words[21] = 12345                                     # not this process's number
+    words[23] = _handle_checksum(words)
+    assert capi.handle_is_local(words) is False
+    words[11] = os.getpid() + 1
+    words[23] = _handle_checksum(words)
+    assert capi.handle_is_local(words) is False
+    words[23] ^= 1
+    with pytest.raises(capi.KvmigError, match="checksum"):
+        capi.handle_is_local(words)
+
+
+@pytest.mark.gpu
+def test_exported_handles_are_local_only_with_their_process_number(built_libs):
+    from distserve_b200 import capi
+
+    pool = torch.zeros(8, 2, 2, 4, 8, dtype=torch.float16, device="cuda")
+    shape = capi.PoolShape.of(*pool.shape, 2)
+    words = capi.get_ipc_mem_handle(pool.data_ptr(), shape)
+    assert words[23] == _handle_checksum(words)           # the test's restatement of the checksum is the library's
+    assert capi.handle_is_local(words) is True
+    forged = list(words)
+    forged[21] ^= 0x55
+    forged[23] = _handle_checksum(forged)
+    assert capi.handle_is_local(forged) is False
+    # registering the forged handle takes the other-process route (CUDA IPC) instead of trusting the raw address:
+    # either CUDA refuses to open a handle of the opening process itself, or the open shows in the counter
+    capi.reset_registry()
+    opened = capi.get_counter("mapped_peers")
+    try:
+        capi.register_ipc_mem_handle(forged, forged, 2, 2, [1, 0, 1, 0], [1, 0, 1, 0])
+    except capi.KvmigError as e:
+        assert e.code == capi.ECUDA and "cudaIpcOpenMemHandle" in str(e)
+    else:
+        assert capi.get_counter("mapped_peers") == opened + 1
+    capi.reset_registry()
+    capi.register_ipc_mem_handle(words, words, 2, 2, [1, 0, 1, 0], [1, 0, 1, 0])
+    assert capi.get_counter("mapped_peers") <= opened + 1     # the genuine handle needed no IPC open
+    capi.reset_registry()
+
+
 @pytest.mark.skipif(torch.cuda.is_available(), reason="checks the no-GPU failure mode")
 def test_compute_fails_loudly_without_a_gpu(built_libs):
     from distserve_b200 import capi

@@ -363,6 +363,7 @@ def test_a_load_that_never_completes_is_reported_not_hung():
                     capi.migrate_wait(capi.migrate_blocks_async(1, 1, src, 1, 1, 0, 0, dst, k.data_ptr(), v.data_ptr(),
                                                                 ds.shape()))
             assert e.value.code == capi.EDEVICE
+            assert "at work unit 1," in str(e.value)      # the launch-wide number of the unit that was lost
             capi.set_option("lose_unit_plus1", 0)
             torch.cuda.synchronize()                      # the context is alive
             migrate_all(cs, ds, src, dst)                 # and the same call now succeeds
