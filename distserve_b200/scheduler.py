@@ -35,13 +35,18 @@ class DecodingStageSchedConfig:
 class DecodingStageFCFSScheduler:
     def __init__(self, sched_config: DecodingStageSchedConfig, parallel_config: ParallelConfig, block_manager: BlockManager,
                  engine_migrate_block_callback: Callable[[MigratingRequest], object],
-                 engine_migrate_blocks_batched_callback: Optional[Callable[[Sequence[MigratingRequest]], object]] = None) -> None:
+                 engine_migrate_blocks_batched_callback: Optional[Callable[[Sequence[MigratingRequest]], object]] = None,
+                 engine_begin_migration_callback: Optional[Callable[[Sequence[MigratingRequest]], object]] = None,
+                 engine_finish_migration_callback: Optional[Callable[[object], object]] = None) -> None:
         assert sched_config.policy == "fcfs", f"can not initialize a FCFS scheduler with policy {sched_config.policy}"
         self.sched_config = sched_config
         self.parallel_config = parallel_config
         self.block_manager = block_manager
         self.engine_migrate_block_callback = engine_migrate_block_callback
         self.engine_migrate_blocks_batched_callback = engine_migrate_blocks_batched_callback
+        self.engine_begin_migration_callback = engine_begin_migration_callback
+        self.engine_finish_migration_callback = engine_finish_migration_callback
+        self._in_flight = None        # (pending migration, its requests) enqueued by post_process_pipelined
         self.unaccepted_queue: List[MigratingRequest] = []
         self.waiting_queue: List[Request] = []
         self.swapped_queue: List[Request] = []
@@ -133,8 +138,14 @@ class DecodingStageFCFSScheduler:
         accepted requests migrate together (one launch per decoding worker)."""
         if self.engine_migrate_blocks_batched_callback is None:
             return self.post_process()
-        waiting = self._waiting_blocks()
-        avail = self.block_manager.get_num_avail_gpu_blocks()
+        chosen = self._choose_acceptable(self._waiting_blocks(), self.block_manager.get_num_avail_gpu_blocks())
+        if chosen:
+            del self.unaccepted_queue[:len(chosen)]
+            self.engine_migrate_blocks_batched_callback(chosen)
+            self.waiting_queue.extend(m.req for m in chosen)
+        return [m.req.request_id for m in chosen]
+
+    def _choose_acceptable(self, waiting: int, avail: int) -> List[MigratingRequest]:
         chosen: List[MigratingRequest] = []
         for m in self.unaccepted_queue:
             n = m.req.get_input_len()
@@ -143,11 +154,37 @@ class DecodingStageFCFSScheduler:
             chosen.append(m)
             waiting += self._blocks(n)
             avail -= self._blocks(n)
+        return chosen
+
+    def post_process_pipelined(self) -> List[int]:
+        """``post_process_batched`` with one group of requests in flight: the group accepted now is enqueued on
+        the workers first, and only then is the group enqueued by the previous call awaited, so the host work of
+        an iteration (this acceptance included) runs while the previous group's copy is on the wire.  Requests
+        join the waiting queue when their own copy has finished, i.e. one call later than with
+        ``post_process_batched``.  The group in flight already holds its target blocks, so it counts against the
+        free blocks of the acceptance rule; it does not count against the waiting-queue threshold, because in the
+        unpipelined flow it would have moved from the waiting queue into a batch by now.  Returns the ids of the
+        requests that became ready in this call."""
+        if self.engine_begin_migration_callback is None or self.engine_finish_migration_callback is None:
+            return self.post_process_batched()
+        chosen = self._choose_acceptable(self._waiting_blocks(), self.block_manager.get_num_avail_gpu_blocks())
+        started = None
         if chosen:
             del self.unaccepted_queue[:len(chosen)]
-            self.engine_migrate_blocks_batched_callback(chosen)
-            self.waiting_queue.extend(m.req for m in chosen)
-        return [m.req.request_id for m in chosen]
+            started = (self.engine_begin_migration_callback(chosen), chosen)
+        ready = self.flush_pipeline()
+        self._in_flight = started
+        return ready
+
+    def flush_pipeline(self) -> List[int]:
+        """Await the group in flight, if any, and hand its requests to the waiting queue."""
+        if self._in_flight is None:
+            return []
+        pending, group = self._in_flight
+        self._in_flight = None
+        self.engine_finish_migration_callback(pending)
+        self.waiting_queue.extend(m.req for m in group)
+        return [m.req.request_id for m in group]
 
     # --- counters -----------------------------------------------------------------------
     def get_processing_num_requests(self) -> int:

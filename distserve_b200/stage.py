@@ -71,6 +71,18 @@ class ContextStageEngine(StageEngine):
         self.block_manager.free_blocks(migrating_req.req.request_id)
 
 
+class PendingMigration:
+    """A group of requests whose copy has been enqueued on every decoding worker but not awaited yet."""
+
+    __slots__ = ("requests", "workers", "tickets", "targets")
+
+    def __init__(self, requests, workers, tickets, targets) -> None:
+        self.requests, self.workers, self.tickets, self.targets = requests, workers, tickets, targets
+
+    def num_blocks(self) -> int:
+        return sum(len(t) for t in self.targets)
+
+
 class DecodingStageEngine(StageEngine):
     def __init__(self, *args, clear_migrated_blocks_callback: Optional[Callable[[MigratingRequest], None]] = None,
                  **kwargs) -> None:
@@ -114,6 +126,13 @@ class DecodingStageEngine(StageEngine):
         launch-and-await round trip, which this removes.  Returns each request's target block ids."""
         if not migrating_reqs:
             return []
+        return self.finish_migrate_blocks_batched(self.begin_migrate_blocks_batched(migrating_reqs))
+
+    def begin_migrate_blocks_batched(self, migrating_reqs: Sequence[MigratingRequest]) -> "PendingMigration":
+        """First half of :meth:`migrate_blocks_batched`: reserve the target blocks and enqueue the copy on every
+        decoding worker, without waiting for it.  The caller may go on with host work (or enqueue the next
+        group) and must call :meth:`finish_migrate_blocks_batched` before the requests join a batch; the
+        context stage's blocks are released only there."""
         ctx_pc = migrating_reqs[0].context_parallel_config
         assert all(m.context_parallel_config.to_list()[::2] == ctx_pc.to_list()[::2] for m in migrating_reqs), \
             "requests of one batch must come from the same context stage layout"
@@ -135,13 +154,18 @@ class DecodingStageEngine(StageEngine):
             targets += target
             self._stamp(req.request_id, "migration_begin")
         workers = [worker for row in self.workers for worker in row]
-        tickets = _resolve([worker.migrate_blocks_async(sources, ctx_pc, targets) for worker in workers])
-        _resolve([worker.migrate_wait(ticket) for worker, ticket in zip(workers, tickets)])
-        for m in migrating_reqs:
+        tickets = [worker.migrate_blocks_async(sources, ctx_pc, targets) for worker in workers]
+        return PendingMigration(list(migrating_reqs), workers, tickets, per_request)
+
+    def finish_migrate_blocks_batched(self, pending: "PendingMigration") -> List[List[int]]:
+        """Second half: wait until every worker has read the sources, then let the context stage recycle them."""
+        tickets = _resolve(pending.tickets)
+        _resolve([worker.migrate_wait(ticket) for worker, ticket in zip(pending.workers, tickets)])
+        for m in pending.requests:
             self._stamp(m.req.request_id, "migration_end")
             if self.clear_migrated_blocks_callback is not None:
                 self.clear_migrated_blocks_callback(m)
-        return per_request
+        return pending.targets
 
     def migration_latency(self, request_id: int) -> float:
         """Seconds between the two stamps, the reference's definition of the

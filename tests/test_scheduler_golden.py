@@ -150,3 +150,59 @@ def test_context_scheduler_replays_reference_decisions(golden_dir):
                         waiting=[len(sched.waiting_queue)] + [r.request_id for r in sched.waiting_queue[:2]],
                         unaccepted=[r.request_id for r in sched.unaccepted_queue], on_fly=sched.num_on_fly_request_block)
             assert mine == ref, f"seed {sc['seed']} iteration {it}: {mine} != {ref}"
+
+
+def test_pipelined_acceptance_accepts_the_same_requests_one_call_later():
+    """post_process_pipelined enqueues the group accepted now before it awaits the group enqueued by the
+    previous call; over a whole run it accepts the requests post_process_batched accepts, in the same order,
+    and every group is begun before the previous one is finished."""
+    from distserve_b200.block_manager import BlockManager
+    from distserve_b200.config import CacheConfig, KVModelConfig, ParallelConfig
+    from distserve_b200.request import MigratingRequest, Request
+    from distserve_b200.scheduler import DecodingStageFCFSScheduler, DecodingStageSchedConfig
+
+    def run(pipelined):
+        pc, cache, model = ParallelConfig(), CacheConfig(16, 1 << 20), KVModelConfig(2, 2, 8)
+        bm = BlockManager("decoding", 256, 1, model, pc, cache, lambda *a: [])
+        log = []
+
+        def begin(group):
+            for m in group:
+                bm.allocate_blocks(Request.of_length(m.req.request_id, m.req.get_input_len()))
+            log.append(("begin", [m.req.request_id for m in group]))
+            return list(group)
+
+        def finish(pending):
+            log.append(("finish", [m.req.request_id for m in pending]))
+
+        def batched(group):
+            finish(begin(group))
+
+        s = DecodingStageFCFSScheduler(DecodingStageSchedConfig(), pc, bm, lambda m: batched([m]), batched,
+                                       begin if pipelined else None, finish if pipelined else None)
+        for rid in range(30):
+            req = Request.of_length(rid, 40 + 7 * rid)
+            req.append_token()
+            s.add_request(MigratingRequest(req, list(range(-(-req.get_input_len() // 16))), pc))
+        ready_order = []
+        for _ in range(200):
+            ready_order += s.post_process_pipelined() if pipelined else s.post_process_batched()
+            batch = s.get_next_batch()
+            for r in list(batch.requests)[:2]:               # two requests finish per iteration
+                r.is_finished = True
+            for q in s.batch_queues:
+                for r in q.pop_finished_requests():
+                    bm.free_blocks(r.request_id)
+            if not s.unaccepted_queue and s._in_flight is None:
+                break
+        return ready_order, log
+
+    plain, _ = run(False)
+    piped, log = run(True)
+    assert plain == piped == list(range(30))
+    # a group is begun before the group ahead of it is finished
+    begins = [i for i, (kind, _) in enumerate(log) if kind == "begin"]
+    finishes = [i for i, (kind, _) in enumerate(log) if kind == "finish"]
+    assert len(begins) == len(finishes) >= 2
+    assert all(log[b][1] == log[f][1] for b, f in zip(begins, finishes))
+    assert any(begins[i + 1] < finishes[i] for i in range(len(begins) - 1))
