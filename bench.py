@@ -89,6 +89,9 @@ def parse_args(argv=None):
     ap.add_argument("--no-other-workloads", action="store_true", help="N=1: skip the short c1 and c5 runs")
     ap.add_argument("--no-overlap", action="store_true", help="N=4/8: skip the serving loop with stand-in decode steps")
     ap.add_argument("--only-value", action="store_true", help="time the value region only (profiler captures)")
+    ap.add_argument("--peer-in-process", action="store_true",
+                    help="one process, two GPUs: every context worker on GPU 0, decoding worker (0,0) on GPU 1 "
+                         "(a single-process cross-GPU case, e.g. for a profiler capture)")
     return ap.parse_args(argv)
 
 
@@ -331,6 +334,29 @@ class _DrivenElsewhere:
 # one workload on the GPU(s)
 # ----------------------------------------------------------------------------------------------
 
+def peer_copy_ceiling(src_device, dst_device, nbytes=1 << 30, repeats=10):
+    """GB/s of one plain device-to-device copy (copy engines, no kernel of this library) between two GPUs of this
+    process: the practical ceiling of the link for a single stream of large transfers."""
+    import torch
+
+    src = torch.empty(nbytes, dtype=torch.uint8, device=f"cuda:{src_device}")
+    dst = torch.empty(nbytes, dtype=torch.uint8, device=f"cuda:{dst_device}")
+    times = []
+    with torch.cuda.device(dst_device):
+        for _ in range(repeats + 2):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            a.record()
+            dst.copy_(src, non_blocking=True)
+            b.record()
+            torch.cuda.synchronize()
+            times.append(a.elapsed_time(b))
+    best = min(times[2:])
+    return {"GBps": nbytes / (best / 1e3) / 1e9, "bytes": nbytes, "repeats": repeats,
+            "call": "torch.Tensor.copy_ between two devices of one process (a driver peer copy on the copy engines), "
+                    "CUDA events on the destination's stream, best of the repeats after 2 warm-up copies"}
+
+
 def run_workload(args, w, world, rank, local_rank, dist, steps, warmup, primary=True):
     import torch
 
@@ -345,7 +371,10 @@ def run_workload(args, w, world, rank, local_rank, dist, steps, warmup, primary=
     from distserve_b200.workloads import make_trace, trace_blocks
 
     trace = make_trace(w)
-    same_device = world == 1
+    peer = bool(args.peer_in_process) and world == 1
+    same_device = world == 1 and not peer
+    ctx_device, dec_device = (0, 1) if peer else (local_rank, local_rank)
+    torch.cuda.set_device(dec_device)
     capi.reset_registry()
 
     def barrier():
@@ -355,30 +384,44 @@ def run_workload(args, w, world, rank, local_rank, dist, steps, warmup, primary=
 
     roles = None if world == 1 else plan_roles(w, world)
     cache = CacheConfig(w.block_size, 1 << 20)
-    ctx_worker = dec_worker = None
+    ctx_workers = {}          # (pp_rank, tp_rank) -> worker; a multi-rank run holds at most one per rank
+    dec_worker = None
     role = Role("both") if roles is None else roles[rank]
 
-    def fill(worker):
-        g = torch.Generator(device="cuda").manual_seed(w.seed * 1000 + rank)
+    def fill(worker, salt):
+        g = torch.Generator(device=worker.device).manual_seed(w.seed * 1000 + salt)
         for pool in (worker.k_cache, worker.v_cache):
             pool.normal_(generator=g)
 
     handles = None
-    if role.stage in ("ctx", "both"):
-        pc = w.ctx_config(role.pp_rank, role.tp_rank)
-        ctx_worker = KVWorker(rank, "context", w.model, cache, pc, device=local_rank)
-        handles = ctx_worker.init_kvcache_and_swap(w.ctx_pool_blocks, 1)
-        fill(ctx_worker)
+    if role.stage == "both":
+        # one process holds the whole context stage and decoding worker (0, 0)
+        table = []
+        for p in range(w.ctx_pp):
+            row = []
+            for t in range(w.ctx_tp):
+                cw = KVWorker(p * w.ctx_tp + t, "context", w.model, cache, w.ctx_config(p, t), device=ctx_device)
+                row.append(cw.init_kvcache_and_swap(w.ctx_pool_blocks, 1))
+                fill(cw, p * w.ctx_tp + t)
+                ctx_workers[(p, t)] = cw
+            table.append(row)
+    elif role.stage == "ctx":
+        cw = KVWorker(rank, "context", w.model, cache, w.ctx_config(role.pp_rank, role.tp_rank), device=ctx_device)
+        handles = cw.init_kvcache_and_swap(w.ctx_pool_blocks, 1)
+        fill(cw, rank)
+        ctx_workers[(role.pp_rank, role.tp_rank)] = cw
     if role.stage in ("dec", "both"):
         pc = w.dec_config(role.pp_rank, role.tp_rank)
-        dec_worker = KVWorker(rank, "decoding", w.model, cache, pc, device=local_rank)
+        dec_worker = KVWorker(rank, "decoding", w.model, cache, pc, device=dec_device)
         dec_worker.init_kvcache_and_swap(w.dec_pool_blocks, 1)
         dec_worker.k_cache.zero_()
         dec_worker.v_cache.zero_()
-    torch.cuda.synchronize()
+    for d in {ctx_device, dec_device}:
+        torch.cuda.synchronize(d)
 
     # handle table [pp][tp] of the context stage, gathered the way the engine gathers it
-    table = [[handles]] if dist is None else exchange_handles(w, roles, handles)
+    if dist is not None:
+        table = exchange_handles(w, roles, handles)
     ctx_pc = w.ctx_config()
     n_replicas = 1 if roles is None else num_replicas(roles)
     my_trace = []
@@ -430,12 +473,17 @@ def run_workload(args, w, world, rank, local_rank, dist, steps, warmup, primary=
         for t in tickets:
             capi.migrate_wait(t)
 
-    def step_e2e(latencies=None):
+    def step_e2e():
+        migrate = dec_worker.migrate_blocks
+        for item in my_trace:
+            migrate(list(item.src_blocks), ctx_pc, list(item.dst_blocks))     # lists are passed by value, as Ray passes them
+
+    def step_e2e_latencies(latencies):
+        """The same calls with a host clock around each (kept out of the throughput region)."""
         for item in my_trace:
             t0 = time.perf_counter()
             dec_worker.migrate_blocks(list(item.src_blocks), ctx_pc, list(item.dst_blocks))
-            if latencies is not None:
-                latencies.append(time.perf_counter() - t0)
+            latencies.append(time.perf_counter() - t0)
 
     # ---- the package's own host API at the batched cadence ----------------------------------------------
     engine = sched = None
@@ -460,21 +508,29 @@ def run_workload(args, w, world, rank, local_rank, dist, steps, warmup, primary=
             for r in q.pop_finished_requests():
                 engine.block_manager.free_blocks(r.request_id)
 
-    def step_engine(launch_counter=None):
+    def arrivals_of_one_step():
+        """What the context stage hands over in one step: a MigratingRequest per request of the trace."""
+        out = []
+        for item in my_trace:
+            req = Request.of_length(item.request_id, item.prompt_len)
+            req.append_token()                                  # the token the prefill step produced
+            out.append(MigratingRequest(req, list(item.src_blocks), ctx_pc))
+        return out
+
+    sources = {item.request_id: item.src_blocks for item in my_trace}
+    # built ahead of the timed region: they are the step's input, produced by the context stage, not by this path
+    prepared_arrivals = [arrivals_of_one_step() for _ in range(max(1, warmup) + steps)] if dec_worker is not None else []
+
+    def step_engine():
         bm = engine.block_manager
         sched.flush_pipeline()
         for rid in list(bm.block_table):
             bm.free_blocks(rid)
         for q in sched.batch_queues:
             q.requests = []
-        sched.waiting_queue, sched.swapped_queue, sched.unaccepted_queue = [], [], []
+        sched.waiting_queue, sched.swapped_queue = [], []
+        sched.unaccepted_queue = prepared_arrivals.pop() if prepared_arrivals else arrivals_of_one_step()
         engine.lifetime_events.clear()
-        sources = {}
-        for item in my_trace:
-            req = Request.of_length(item.request_id, item.prompt_len)
-            req.append_token()                                  # the token the prefill step produced
-            sched.add_request(MigratingRequest(req, list(item.src_blocks), ctx_pc))
-            sources[item.request_id] = item.src_blocks
         floor = int(0.15 * w.dec_pool_blocks)
         while sched.unaccepted_queue or sched._in_flight is not None:
             while bm.get_num_avail_gpu_blocks() < floor and sched.get_processing_num_requests():
@@ -512,7 +568,7 @@ def run_workload(args, w, world, rank, local_rank, dist, steps, warmup, primary=
     def snapshot():
         return {k: capi.get_counter(k) for k in host_counters}
 
-    sampler = ClockSampler(local_rank)
+    sampler = ClockSampler(dec_device)
     if primary and (rank == 0 or (roles is not None and roles[rank] == Role("dec", 0, 0, 0))):
         sampler.start()
     for _ in range(warmup):
@@ -531,8 +587,11 @@ def run_workload(args, w, world, rank, local_rank, dist, steps, warmup, primary=
     if not args.only_value:
         if not args.no_e2e:
             c0 = snapshot()
-            ms_e2e = timed(step_e2e, steps, latencies=latencies)[0]
+            ms_e2e = timed(step_e2e, steps)[0]
             c1 = snapshot()
+            if dec_worker is not None:
+                step_e2e_latencies(latencies)
+                torch.cuda.synchronize()
             calls = max(1, c1["migrate_calls"] - c0["migrate_calls"])
             host_us = {k[3:]: (c1[k] - c0[k]) / calls / 1e3 for k in host_counters if k.startswith("ns_")}
             host_us["plan_reused"] = (c1["plan_cache_hits"] - c0["plan_cache_hits"]) / calls
@@ -550,11 +609,10 @@ def run_workload(args, w, world, rank, local_rank, dist, steps, warmup, primary=
             samples = spotcheck.plan_samples(w, roles, trace)
         else:
             samples = spotcheck.plan_samples(w, roles, trace, traces_by_rank=records_by_rank)
-        read_source = spotcheck.torch_pool_reader(ctx_worker.k_cache, ctx_worker.v_cache) if ctx_worker is not None else None
-        if roles is None and ctx_worker is not None:
-            read_source = {(0, 0): read_source}
+        read_source = {key: spotcheck.torch_pool_reader(cw.k_cache, cw.v_cache) for key, cw in ctx_workers.items()} or None
         read_target = spotcheck.torch_pool_reader(dec_worker.k_cache, dec_worker.v_cache) if dec_worker is not None else None
-        torch.cuda.synchronize()
+        for d in {ctx_device, dec_device}:
+            torch.cuda.synchronize(d)
         readbacks = spotcheck.exchange_samples(samples, rank, read_source, read_target, dist)
         n_samples, n_blocks, bad = check_readbacks(w, readbacks)
         stats = torch.tensor([float(n_samples), float(n_blocks), float(len(bad))], dtype=torch.float64)
@@ -562,10 +620,9 @@ def run_workload(args, w, world, rank, local_rank, dist, steps, warmup, primary=
             dist.all_reduce(stats)
         return int(stats[0].item()), int(stats[1].item()), int(stats[2].item()), bad
 
-    single_gpu_complete = same_device and (w.ctx_tp, w.ctx_pp) == (1, 1)
     verified = None
     verification = None
-    if not args.only_value and (not same_device or single_gpu_complete):
+    if not args.only_value:
         n_samples, n_blocks, n_bad, bad = verify()
         untouched_ok = True
         if untouched:
@@ -592,7 +649,7 @@ def run_workload(args, w, world, rank, local_rank, dist, steps, warmup, primary=
         ms_engine = timed(step_engine, steps)[0]
         engine_launches = capi.get_counter("kernel_launches") - l0
         launches += engine_launches
-        if not same_device or single_gpu_complete:
+        if True:
             records = [spotcheck.TraceItem(rid, 0, src, dst) for rid, src, dst in engine_records]
             if dist is not None:
                 gathered = [None] * world
@@ -719,6 +776,7 @@ def run_workload(args, w, world, rank, local_rank, dist, steps, warmup, primary=
                 "algorithmic_bytes_per_launch": worst[2], "per": "slowest destination GPU",
                 "kernel": kernel_label}
 
+    peer_copy = peer_copy_ceiling(ctx_device, dec_device) if peer and primary and not args.only_value else None
     out = {
         "workload": w, "trace": trace, "same_device": same_device, "n_dest": n_dest, "n_replicas": n_replicas,
         "value": gbs(ms_value), "ms_value": ms_value, "e2e_value": gbs(ms_e2e), "ms_e2e": ms_e2e,
@@ -727,9 +785,10 @@ def run_workload(args, w, world, rank, local_rank, dist, steps, warmup, primary=
         "p50_ms": p50[0].item() * 1e3 if lat or dist is not None else None,
         "roofline": roof, "launches": int(totals[1].item()), "clocks": clocks, "verified": verified,
         "verification": verification, "engine_verification": engine_verification, "swap": swap_info, "host_us": host_us,
+        "peer_copy": peer_copy,
     }
     # release the pools before another workload is set up in this process
-    del ctx_worker, dec_worker, engine, sched
+    del ctx_workers, dec_worker, engine, sched
     capi.reset_registry()
     torch.cuda.empty_cache()
     return out
@@ -770,7 +829,7 @@ def main():
         w = w.scaled(ctx_pool_blocks=args.pool_blocks, dec_pool_blocks=args.pool_blocks)
     if args.requests:
         w = w.scaled(num_requests=args.requests)
-    same_device = args.gpus == 1
+    same_device = args.gpus == 1 and not args.peer_in_process
 
     if args.impl == "reference":
         if rank != 0:
@@ -809,7 +868,7 @@ def main():
 
     # N = 1: the launch-bound regimes (small requests) beside the headline workload, a few steps each
     others = None
-    if same_device and not args.no_other_workloads and not args.only_value and args.workload is None:
+    if same_device and world == 1 and not args.no_other_workloads and not args.only_value and args.workload is None:
         others = {}
         for other in ("c1", "c5"):
             o = run_workload(args, WORKLOADS[other], world, rank, local_rank, dist, max(3, min(args.steps, 10)), 3, primary=False)
@@ -817,7 +876,7 @@ def main():
                              "batched": o["batched_value"], "e2e_batched": o["engine_value"], "unit": UNIT,
                              "p50_migrate_latency_ms": o["p50_ms"], "avg_launch_us": o["roofline"]["avg_launch_us"],
                              "verified_on_device": o["verified"], "steps": max(3, min(args.steps, 10)),
-                             "note": "context rank 0 -> decoding rank 0 of the layout, both pools on this GPU"}
+                             "note": "the whole context stage -> decoding worker (0, 0) of the layout, all pools on this GPU"}
 
     # N = 4 / 8: the serving loop of the end-to-end configuration, one worker process per GPU, driven from rank 0
     overlap = None
@@ -882,6 +941,10 @@ def main():
                                       "target blocks from the block manager"}
     if r["swap"] is not None:
         line["swap"] = r["swap"]
+    if r["peer_copy"] is not None:
+        line["roofline"]["measured_peer_copy"] = r["peer_copy"]
+        line["roofline"]["frac_of_measured_peer_copy"] = r["roofline"]["achieved"] / r["peer_copy"]["GBps"]
+        line["config"]["workload"] += " (one process: context stage on GPU 0, decoding worker (0,0) on GPU 1)"
     if others is not None:
         line["other_workloads"] = others
     if overlap is not None:
