@@ -86,7 +86,7 @@ int64_t handle_checksum(const int64_t* w) {
 // 96 KiB.  Anything from 16 KiB in flight per SM upward saturates NVLink.
 struct Options {
     std::atomic<int64_t> kernel{0}, chunk_bytes{16384}, stages{3}, ctas_per_sm{0}, inline_tables{1}, overlap_launches{1}, max_ctas{0}, l2_hint{0},
-        dynamic_units{1}, wait_limit_ms{2000}, lose_unit_plus1{0}, unit_batch{0};
+        dynamic_units{1}, wait_limit_ms{2000}, lose_unit_plus1{0}, unit_batch{0}, swap_wait{-1};
 };
 Options g_opt;
 std::atomic<uint64_t> g_option_gen{1};   // bumped by every kvmig_set_option
@@ -1199,6 +1199,13 @@ int kvmig_swap(const int64_t* src_ids, int64_t n_src, const int64_t* dst_ids, in
                         (long long)dst_ids[i], is_swap_in ? "GPU" : "host", (long long)dst_limit);
     }
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    // "swap_wait": -1 until first use, then taken from the environment unless the option was set explicitly.
+    int64_t swap_wait = g_opt.swap_wait.load();
+    if (swap_wait < 0) {
+        const char* env = std::getenv("KVMIG_SWAP_WAIT");
+        swap_wait = (env && env[0] && env[0] != '0') ? 1 : 0;
+        g_opt.swap_wait.store(swap_wait);
+    }
     const int64_t bb = block_bytes(*shape);
     const cudaMemcpyKind kind = is_swap_in ? cudaMemcpyHostToDevice : cudaMemcpyDeviceToHost;
     char* src_pool[2] = {static_cast<char*>(is_swap_in ? k_swap : k_cache), static_cast<char*>(is_swap_in ? v_swap : v_cache)};
@@ -1215,6 +1222,7 @@ int kvmig_swap(const int64_t* src_ids, int64_t n_src, const int64_t* dst_ids, in
         g_cnt.bytes_swapped += 2 * (j - i) * bb;
         i = j;
     }
+    if (swap_wait && n_src > 0) CU_TRY(cudaStreamSynchronize(stream));
     return 0;
 }
 
@@ -1232,6 +1240,7 @@ static std::atomic<int64_t>* option_slot(const char* name) {
     if (!std::strcmp(name, "wait_limit_ms")) return &g_opt.wait_limit_ms;
     if (!std::strcmp(name, "unit_batch")) return &g_opt.unit_batch;
     if (!std::strcmp(name, "lose_unit_plus1")) return &g_opt.lose_unit_plus1;
+    if (!std::strcmp(name, "swap_wait")) return &g_opt.swap_wait;
     return nullptr;
 }
 

@@ -238,6 +238,16 @@ KVMIG_API int kvmig_migrate_blocks_static(int64_t ctx_pp_size, int64_t ctx_tp_si
  * source[i] -> host block target[i].  `shape` describes the GPU pools; the
  * host pools have the same per-block shape and num_cpu_blocks blocks
  * (distserve/worker.py:122-130).
+ *
+ * The reference worker records the event it later waits on BEFORE it calls
+ * this operator (distserve/worker.py:286-287 vs 302-311), so with the
+ * unmodified worker neither wait_for_all_swap_in/out nor the per-request wait
+ * in step() covers the copies; a deployment on that worker relies on a stream
+ * or device synchronize, or sets the option "swap_wait" (environment variable
+ * KVMIG_SWAP_WAIT=1 for hosts that cannot call kvmig_set_option), which makes
+ * this call return only after its copies have finished.  Off by default: the
+ * copies then overlap whatever the caller does next, which is the point of
+ * running them on a side stream.
  */
 KVMIG_API int kvmig_swap(const int64_t* source_block_ids, int64_t num_source,
                const int64_t* target_block_ids, int64_t num_target,
@@ -271,7 +281,10 @@ KVMIG_API int kvmig_swap(const int64_t* source_block_ids, int64_t num_source,
  *             call fail with KVMIG_EDEVICE (default 2000),
  *             "lose_unit_plus1" N > 0 = failure-path exercise: work unit N-1
  *             arms its completion barrier but never issues its load, so that
- *             wait runs out (default 0)
+ *             wait runs out (default 0),
+ *             "swap_wait" 1 = kvmig_swap returns only after its copies have
+ *             finished (default 0, or the value of KVMIG_SWAP_WAIT in the
+ *             environment when the option was never set)
  *   counters: "kernel_launches", "memcpy_calls", "bytes_migrated",
  *             "bytes_swapped", "mapped_peers", "migrate_calls",
  *             "plan_cache_hits" (calls that reused the previous call's
