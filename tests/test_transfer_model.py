@@ -36,3 +36,35 @@ def test_same_gpu_model_and_limits():
     short = T.effective_GBps(16, w.model, w.dec_config())       # one block: dominated by the fixed cost
     long_ = T.effective_GBps(2048, w.model, w.dec_config())
     assert short < 0.5 * long_ < 0.5 * T.NVLINK5.payload_GBps + 1
+
+
+def test_charging_the_transfer_changes_the_placement():
+    """The reference's simulator hands a request from prefill to decode with no delay, so a search on it prefers
+    whatever decodes most cheaply; once the hand-off is charged, a stage that pulls over a slow link needs more
+    workers (each pulls a smaller share), and the choice flips.  Over NVLink the transfer is too short to matter."""
+    w = WORKLOADS["c2"]
+    lens = [t.prompt_len for t in make_trace(w)]
+    slow = [T.DecodePlacement(1, 1, T.CROSS_NODE_400G, goodput_per_gpu=1.00),
+            T.DecodePlacement(2, 1, T.CROSS_NODE_400G, goodput_per_gpu=0.93),
+            T.DecodePlacement(4, 1, T.CROSS_NODE_400G, goodput_per_gpu=0.85)]
+    free, delay = T.pick_decode_placement(slow, lens, w.model, max_handoff_ms=10.0, charge_transfer=False)
+    assert (free.tp, free.pp, delay) == (1, 1, 0.0)
+    charged, delay = T.pick_decode_placement(slow, lens, w.model, max_handoff_ms=10.0, charge_transfer=True)
+    assert (charged.tp, charged.pp) == (4, 1) and 5.0 < delay <= 10.0
+    # streaming the KV during prefill leaves only the last group after prefill ends: the cheapest layout fits again
+    streamed, delay = T.pick_decode_placement(slow, lens, w.model, max_handoff_ms=10.0, streamed_groups=8)
+    assert (streamed.tp, streamed.pp) == (1, 1) and delay < 10.0
+    fast = [T.DecodePlacement(c.tp, c.pp, T.NVLINK5, c.goodput_per_gpu) for c in slow]
+    nv, delay = T.pick_decode_placement(fast, lens, w.model, max_handoff_ms=10.0)
+    assert (nv.tp, nv.pp) == (1, 1) and delay < 2.5
+    with pytest.raises(ValueError):
+        T.pick_decode_placement(slow, lens, w.model, max_handoff_ms=1.0)
+
+
+def test_exit_prefill_delay_is_the_awaited_migration_in_milliseconds():
+    w = WORKLOADS["c4"]
+    dec = w.dec_config()
+    assert T.exit_prefill_delay_ms(1024, w.model, dec) == pytest.approx(T.migration_seconds(1024, w.model, dec) * 1e3)
+    assert T.exit_prefill_delay_ms(0, w.model, dec) == 0.0
+    whole = T.exit_prefill_delay_ms(4096, w.model, dec)
+    assert T.exit_prefill_delay_ms(4096, w.model, dec, streamed_groups=8) < whole / 4

@@ -6,8 +6,9 @@ cudaMalloc can fail or stall the device mid-loop, and some embedders forbid
 allocation after start-up.  For them the library offers the same copy with its
 scratch (block tables, status word) in a fixed array that is part of the loaded
 module.  This file checks, through the C ABI, that the variant writes exactly
-what the ordinary entry point writes — on two calls in a row, the second
-shorter than the first so that stale table contents would show — that device
+what the ordinary entry point writes and what the CPU oracle computes — on two
+calls in a row, the second shorter than the first so that stale table contents
+would show — that device
 memory in use does not change across the calls, and that oversize requests
 are refused.  It is collected last on purpose.
 """
@@ -16,7 +17,7 @@ import pytest
 import torch
 
 from distserve_b200 import capi
-from tests.kvutil import Stage, register_all
+from tests.kvutil import Stage, assert_stage_equals_host, oracle_all, register_all
 
 pytestmark = pytest.mark.gpu
 
@@ -44,6 +45,7 @@ def test_static_entry_point_matches_the_ordinary_one_twice_in_a_row(ctx_layout, 
     assert pools_equal(ordinary, static)
     pull(capi.migrate_blocks, ctx, ordinary, [0], [0])              # loads the module's kernels before memory is sampled
     pull(capi.migrate_blocks_static, ctx, static, [0], [0])         # first call: looks up the array's address
+    oracle_all(ctx, static, [0], [0])
     for n in (257, 9):                                              # two calls in a row; the second reuses the array
         src = [int(x) for x in rng.integers(0, 300, size=n)]
         dst = [int(x) for x in rng.permutation(280)[:n]]
@@ -54,6 +56,9 @@ def test_static_entry_point_matches_the_ordinary_one_twice_in_a_row(ctx_layout, 
         torch.cuda.synchronize()
         assert torch.cuda.mem_get_info()[0] == free_before, "device memory in use changed across the static call"
         assert pools_equal(ordinary, static), f"pools differ after the call with {n} blocks"   # bit-exact, no tolerance
+        # and both equal what the CPU oracle computes for the same call (the host copies start out equal too)
+        oracle_all(ctx, static, src, dst)
+        assert_stage_equals_host(static, f"static entry point, {n} blocks")
 
 
 def test_static_entry_point_limits_and_refusals():
