@@ -73,6 +73,8 @@ class KVModelConfig:
 
     def get_num_heads(self, parallel_config: ParallelConfig = ParallelConfig()) -> int:
         tp = parallel_config.tensor_parallel_size
+        if self.num_kv_heads == 1:
+            return 1      # multi-query attention: every rank holds the one KV head (distserve/config.py:233-237)
         if self.num_kv_heads % tp:
             raise ValueError(f"{self.num_kv_heads} KV heads do not split over {tp} tensor-parallel ranks")
         return self.num_kv_heads // tp
@@ -96,6 +98,8 @@ class KVModelConfig:
     def head_range(self, pc: ParallelConfig) -> Tuple[int, int]:
         """Global KV heads held by a worker: tensor rank i holds the i-th chunk."""
         n = self.get_num_heads(pc)
+        if self.num_kv_heads == 1:
+            return 0, 1
         return pc.tensor_parallel_rank * n, (pc.tensor_parallel_rank + 1) * n
 
     def block_bytes(self, pc: ParallelConfig, block_size: int) -> int:
@@ -122,8 +126,12 @@ def plan_overlaps(model: KVModelConfig, ctx: ParallelConfig, dec: ParallelConfig
     dl0, dl1 = model.layer_range(dec)
     dh0, dh1 = model.head_range(dec)
     out: List[Overlap] = []
+    # With a single KV head every context rank holds it; a decoding rank reads the replica at the matching position.
+    replica = dec.tensor_parallel_rank * ctx.tensor_parallel_size // dec.tensor_parallel_size
     for p in range(ctx.pipeline_parallel_size):
         for t in range(ctx.tensor_parallel_size):
+            if model.num_kv_heads == 1 and t != replica:
+                continue
             c = ctx.with_rank(p, t)
             cl0, cl1 = model.layer_range(c)
             ch0, ch1 = model.head_range(c)

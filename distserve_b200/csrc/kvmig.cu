@@ -323,9 +323,14 @@ struct SegPlan {
     int64_t src_layer_off, dst_layer_off, n_layers, src_head_off, dst_head_off, n_heads;
 };
 
+// KV heads a worker of a tp-way stage holds: H/tp — or the single head of a multi-query model, which every
+// tensor-parallel rank holds in full (distserve/config.py:233-237 returns 1 whatever the parallel config).
+inline int64_t local_heads(int64_t H, int64_t tp) { return H == 1 ? 1 : H / tp; }
+
 // Which context workers feed decoding worker (t_d, p_d), and with which sub-rectangles.
 // Worker (tp, t, pp, p) owns layers [p*L/pp, (p+1)*L/pp) and heads [t*H/tp, (t+1)*H/tp)
-// (distserve/config.py:244-257,279-286).
+// (distserve/config.py:244-257,279-286).  With a single KV head every rank holds head 0; decoding rank t_d then
+// reads it from context rank floor(t_d * ctx_tp / dec_tp), which spreads the readers over the replicas.
 int plan_segments(int64_t L, int64_t H, int64_t ctx_tp, int64_t ctx_pp, int64_t dec_tp, int64_t t_d, int64_t dec_pp,
                   int64_t p_d, std::vector<SegPlan>* out) {
     if (L <= 0 || H <= 0) return fail(KVMIG_EINVAL, "num_layers and num_heads must be positive");
@@ -333,15 +338,24 @@ int plan_segments(int64_t L, int64_t H, int64_t ctx_tp, int64_t ctx_pp, int64_t 
     if (L % ctx_pp || L % dec_pp)
         return fail(KVMIG_EINVAL, "num_layers %lld is not divisible by the pipeline-parallel sizes (%lld, %lld)", (long long)L,
                     (long long)ctx_pp, (long long)dec_pp);
-    if (H % ctx_tp || H % dec_tp)
+    const bool replicated = H == 1;
+    if (!replicated && (H % ctx_tp || H % dec_tp))
         return fail(KVMIG_EINVAL, "num_heads %lld is not divisible by the tensor-parallel sizes (%lld, %lld)", (long long)H,
                     (long long)ctx_tp, (long long)dec_tp);
     if (t_d < 0 || t_d >= dec_tp || p_d < 0 || p_d >= dec_pp) return fail(KVMIG_EINVAL, "decoding rank out of range");
-    const int64_t Ld = L / dec_pp, Hd = H / dec_tp, Lc = L / ctx_pp, Hc = H / ctx_tp;
-    const int64_t gl0 = p_d * Ld, gl1 = gl0 + Ld, gh0 = t_d * Hd, gh1 = gh0 + Hd;
+    const int64_t Ld = L / dec_pp, Hd = local_heads(H, dec_tp), Lc = L / ctx_pp, Hc = local_heads(H, ctx_tp);
+    const int64_t gl0 = p_d * Ld, gl1 = gl0 + Ld, gh0 = replicated ? 0 : t_d * Hd, gh1 = gh0 + Hd;
     out->clear();
     for (int64_t p = gl0 / Lc; p * Lc < gl1; ++p) {
         int64_t la = std::max(gl0, p * Lc), lb = std::min(gl1, (p + 1) * Lc);
+        if (replicated) {
+            SegPlan s;
+            s.ctx = CtxKey{ctx_tp, ctx_pp, p, t_d * ctx_tp / dec_tp};
+            s.src_layer_off = la - p * Lc; s.dst_layer_off = la - gl0; s.n_layers = lb - la;
+            s.src_head_off = 0; s.dst_head_off = 0; s.n_heads = 1;
+            out->push_back(s);
+            continue;
+        }
         for (int64_t t = gh0 / Hc; t * Hc < gh1; ++t) {
             int64_t ha = std::max(gh0, t * Hc), hb = std::min(gh1, (t + 1) * Hc);
             SegPlan s;
@@ -352,6 +366,15 @@ int plan_segments(int64_t L, int64_t H, int64_t ctx_tp, int64_t ctx_pp, int64_t 
         }
     }
     return 0;
+}
+
+// The model's global KV-head count, which the migrate call does not carry: heads held locally x dec_tp — unless
+// the registered context stage says the model has a single KV head, which every rank then holds.
+int64_t global_heads(const DeviceState& st, const kvmig_pool_shape* shape, int64_t ctx_tp, int64_t ctx_pp, int64_t dec_tp) {
+    if (shape->num_heads == 1 && dec_tp > 1)
+        for (const auto& kv : st.registry)
+            if (kv.first.tp == ctx_tp && kv.first.pp == ctx_pp) return kv.second.H == 1 ? 1 : shape->num_heads * dec_tp;
+    return shape->num_heads * dec_tp;
 }
 
 constexpr int kWorkPairs = 16;
@@ -437,7 +460,7 @@ int assemble_segments(DeviceState& st, int dev, const std::vector<SegPlan>& plan
                       int64_t ctx_pp, const kvmig_pool_shape* shape, void* k_cache, void* v_cache, bool map_missing,
                       Assembly* out) {
     const int64_t slab = shape->block_size * shape->head_dim * shape->elem_size;
-    const int64_t Lc = L / ctx_pp, Hc = H / ctx_tp;
+    const int64_t Lc = L / ctx_pp, Hc = local_heads(H, ctx_tp);
     for (const SegPlan& sp : plan) {
         auto it = st.registry.find(sp.ctx);
         if (it == st.registry.end())
@@ -672,7 +695,7 @@ int enqueue_migration(int64_t ctx_pp, int64_t ctx_tp, const int64_t* ctx_blocks,
         g_cnt.plan_cache_hits++;
     } else {
         pr.valid = false;
-        const int64_t L = shape->num_layers * dec_pp, H = shape->num_heads * dec_tp;
+        const int64_t L = shape->num_layers * dec_pp, H = global_heads(st, shape, ctx_tp, ctx_pp, dec_tp);
         std::vector<SegPlan> plan;
         rc = plan_segments(L, H, ctx_tp, ctx_pp, dec_tp, dec_tp_rank, dec_pp, dec_pp_rank, &plan);
         if (rc) return rc;
@@ -962,7 +985,7 @@ int migrate_static(int64_t ctx_pp, int64_t ctx_tp, const int64_t* ctx_blocks, in
     rc = static_scratch_for_current_device(dev, &scratch);
     if (rc) return rc;
 
-    const int64_t L = shape->num_layers * dec_pp, H = shape->num_heads * dec_tp;
+    const int64_t L = shape->num_layers * dec_pp, H = global_heads(st, shape, ctx_tp, ctx_pp, dec_tp);
     std::vector<SegPlan> plan;
     rc = plan_segments(L, H, ctx_tp, ctx_pp, dec_tp, dec_tp_rank, dec_pp, dec_pp_rank, &plan);
     if (rc) return rc;
@@ -1101,12 +1124,13 @@ int kvmig_register_ipc_mem_handle(const int64_t* k_handle, int64_t k_len, const 
     kvmig_pool_shape sk = shape_of_handle(k_handle), sv = shape_of_handle(v_handle);
     if (std::memcmp(&sk.num_layers, &sv.num_layers, sizeof(int64_t) * 5) != 0)
         return fail(KVMIG_EINVAL, "K and V pool handles describe different block shapes");
-    if (sk.num_layers != num_layers / ctx_pp || sk.num_heads != num_heads / ctx_tp)
+    if (sk.num_layers != num_layers / ctx_pp || sk.num_heads != local_heads(num_heads, ctx_tp))
         return fail(KVMIG_EINVAL,
                     "exported pool holds %lld layers x %lld heads, but a tp=%lld,pp=%lld worker of a %lld-layer %lld-head model "
                     "holds %lld x %lld",
                     (long long)sk.num_layers, (long long)sk.num_heads, (long long)ctx_tp, (long long)ctx_pp,
-                    (long long)num_layers, (long long)num_heads, (long long)(num_layers / ctx_pp), (long long)(num_heads / ctx_tp));
+                    (long long)num_layers, (long long)num_heads, (long long)(num_layers / ctx_pp),
+                    (long long)local_heads(num_heads, ctx_tp));
 
     std::lock_guard<std::mutex> lock(g_mu);
     DeviceState* stp;

@@ -29,9 +29,13 @@ int kv_oracle_migrate(const uint8_t* const* ctx_k, const uint8_t* const* ctx_v,
 {
     if (n_ctx != n_dec || n_ctx < 0) return -1;
     if (ctx_tp <= 0 || ctx_pp <= 0 || dec_tp <= 0 || dec_pp <= 0) return -1;
-    if (num_layers % ctx_pp || num_layers % dec_pp || num_heads % ctx_tp || num_heads % dec_tp) return -1;
-    const int64_t Ld = num_layers / dec_pp, Hd = num_heads / dec_tp;
-    const int64_t Lc = num_layers / ctx_pp, Hc = num_heads / ctx_tp;
+    /* Multi-query attention: the one KV head is held by every tensor-parallel rank of either stage
+     * (distserve/config.py:233-237); a decoding rank reads the replica at the matching position. */
+    const int replicated = num_heads == 1;
+    if (num_layers % ctx_pp || num_layers % dec_pp) return -1;
+    if (!replicated && (num_heads % ctx_tp || num_heads % dec_tp)) return -1;
+    const int64_t Ld = num_layers / dec_pp, Hd = replicated ? 1 : num_heads / dec_tp;
+    const int64_t Lc = num_layers / ctx_pp, Hc = replicated ? 1 : num_heads / ctx_tp;
     const int64_t dst_block = Ld * Hd * slab_bytes, src_block = Lc * Hc * slab_bytes;
 
 #pragma omp parallel for collapse(2) schedule(static)
@@ -41,8 +45,9 @@ int kv_oracle_migrate(const uint8_t* const* ctx_k, const uint8_t* const* ctx_v,
             const int64_t cp = gl / Lc, cl = gl % Lc;          /* owning pipeline rank, its local layer */
             int64_t dh = 0;
             while (dh < Hd) {
-                const int64_t gh = dec_tp_rank * Hd + dh;      /* global head */
-                const int64_t ct = gh / Hc, ch = gh % Hc;      /* owning tensor rank, its local head */
+                const int64_t gh = replicated ? 0 : dec_tp_rank * Hd + dh;      /* global head */
+                const int64_t ct = replicated ? dec_tp_rank * ctx_tp / dec_tp : gh / Hc;   /* owning (or replica) tensor rank */
+                const int64_t ch = gh % Hc;                                       /* its local head */
                 int64_t run = Hc - ch;                         /* heads left in that owner's chunk ... */
                 if (run > Hd - dh) run = Hd - dh;              /* ... and in this worker's range */
                 const int64_t w = cp * ctx_tp + ct;

@@ -73,14 +73,19 @@ def migrate_blocks_elementwise(
     if len(ctx_blocks) != len(dec_blocks):
         raise ValueError("block index lists differ in length")
     l_per_dec = num_layers // dec_pp
-    h_per_dec = num_heads // dec_tp
+    h_per_dec = 1 if num_heads == 1 else num_heads // dec_tp
     for src_id, dst_id in zip(ctx_blocks, dec_blocks):
         for dl in range(l_per_dec):
             gl = dec_pp_rank * l_per_dec + dl
             c_pp_rank, cl = _owner(gl, num_layers, ctx_pp)
             for dh in range(h_per_dec):
-                gh = dec_tp_rank * h_per_dec + dh
-                c_tp_rank, ch = _owner(gh, num_heads, ctx_tp)
+                if num_heads == 1:
+                    # Multi-query attention: every tensor-parallel rank of either stage holds the one KV head
+                    # (distserve/config.py:233-237); which replica is read does not change the result.
+                    c_tp_rank, ch = dec_tp_rank * ctx_tp // dec_tp, 0
+                else:
+                    gh = dec_tp_rank * h_per_dec + dh
+                    c_tp_rank, ch = _owner(gh, num_heads, ctx_tp)
                 src_k, src_v = ctx_pools[(c_pp_rank, c_tp_rank)]
                 k_cache[dst_id, dl, dh] = src_k[src_id, cl, ch]
                 v_cache[dst_id, dl, dh] = src_v[src_id, cl, ch]
@@ -91,12 +96,25 @@ def _overlaps(num_layers, num_heads, ctx_tp, ctx_pp, dec_tp, dec_tp_rank, dec_pp
     slices to read and to write.  Derived by walking the global (layer, head)
     plane in the decoding worker's own order and cutting wherever the owning
     context worker changes."""
-    for total, parts in ((num_layers, dec_pp), (num_layers, ctx_pp), (num_heads, dec_tp), (num_heads, ctx_tp)):
+    checks = [(num_layers, dec_pp), (num_layers, ctx_pp)] + ([] if num_heads == 1 else [(num_heads, dec_tp), (num_heads, ctx_tp)])
+    for total, parts in checks:
         if total % parts != 0:
             raise ValueError(f"{total} is not divisible by {parts}")
-    l_per_dec, h_per_dec = num_layers // dec_pp, num_heads // dec_tp
-    l_per_ctx, h_per_ctx = num_layers // ctx_pp, num_heads // ctx_tp
-    gl0, gh0 = dec_pp_rank * l_per_dec, dec_tp_rank * h_per_dec
+    l_per_dec, l_per_ctx = num_layers // dec_pp, num_layers // ctx_pp
+    gl0 = dec_pp_rank * l_per_dec
+    if num_heads == 1:
+        # Multi-query attention (distserve/config.py:233-237): one KV head on every rank; read the replica at the
+        # matching position of the context stage.
+        t = dec_tp_rank * ctx_tp // dec_tp
+        g = gl0
+        while g < gl0 + l_per_dec:
+            p = g // l_per_ctx
+            end = min(gl0 + l_per_dec, (p + 1) * l_per_ctx)
+            yield (p, t), (slice(g - p * l_per_ctx, end - p * l_per_ctx), slice(0, 1)), (slice(g - gl0, end - gl0), slice(0, 1))
+            g = end
+        return
+    h_per_dec, h_per_ctx = num_heads // dec_tp, num_heads // ctx_tp
+    gh0 = dec_tp_rank * h_per_dec
 
     def cuts(g0, n, per):
         out, g = [], g0

@@ -31,7 +31,7 @@ class Stage:
         self.dev = {}
         for p in range(pp):
             for t in range(tp):
-                shape = (num_blocks, L // pp, H // tp, B, D)
+                shape = (num_blocks, L // pp, 1 if H == 1 else H // tp, B, D)     # one KV head: every rank holds it
                 hk = host_pool([seed, p, t, 0], shape, elem_size)
                 hv = host_pool([seed, p, t, 1], shape, elem_size)
                 self.host[(p, t)] = (hk, hv)

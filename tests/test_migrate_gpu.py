@@ -372,3 +372,21 @@ def test_a_load_that_never_completes_is_reported_not_hung():
             capi.set_option(name, value)
     oracle_all(cs, ds, src, dst)
     assert_stage_equals_host(ds)
+
+
+@pytest.mark.parametrize("L,ctx,dec", [(4, (2, 1), (1, 1)), (4, (1, 1), (2, 1)), (4, (2, 2), (2, 1)), (6, (4, 1), (2, 3)),
+                                       (6, (2, 3), (4, 1))])
+def test_single_kv_head_models_migrate_from_the_matching_replica(L, ctx, dec):
+    """Multi-query attention: every tensor-parallel rank of both stages holds the model's one KV head
+    (distserve/config.py:233-237).  The pools' replicas are given different contents, so the comparison with the
+    oracle also pins WHICH replica a decoding rank reads."""
+    rng = np.random.default_rng(L + 17)
+    cs = Stage(L, 1, ctx[0], ctx[1], 23, 4, 16, seed=80)
+    ds = Stage(L, 1, dec[0], dec[1], 19, 4, 16, seed=81)
+    assert cs.dev[(0, 0)][0].shape[2] == 1 and ds.dev[(0, 0)][0].shape[2] == 1
+    register_all(cs, ds)
+    for n in (1, 7, 19):
+        src, dst = ragged_lists(rng, 23, 19, n)
+        migrate_all(cs, ds, src, dst)
+        oracle_all(cs, ds, src, dst)
+        assert_stage_equals_host(ds, f"n={n}")

@@ -144,3 +144,51 @@ def test_c_oracle_swap_and_refusals_agree_with_numpy():
         OC.migrate_blocks_c(ctx, 1, 1, [0, 1], 1, 0, 1, 0, [0], k, k.copy(), 2, 2)
     with pytest.raises(ValueError):
         OC.migrate_blocks_c(ctx, 1, 1, [0], 3, 0, 1, 0, [0], k, k.copy(), 2, 2)
+
+
+MQA_LAYOUTS = [
+    # L, (ctx_tp, ctx_pp), (dec_tp, dec_pp) for a model with ONE KV head (multi-query attention)
+    (4, (2, 1), (1, 1)),
+    (4, (1, 1), (2, 1)),
+    (4, (2, 2), (2, 1)),
+    (6, (4, 1), (2, 3)),
+    (6, (2, 3), (4, 1)),
+]
+
+
+@pytest.mark.parametrize("L,ctx,dec", MQA_LAYOUTS)
+def test_single_kv_head_is_held_by_every_rank(L, ctx, dec):
+    """Multi-query attention: ModelConfig.get_num_heads returns 1 whatever the tensor-parallel size
+    (distserve/config.py:233-237), so every rank of both stages holds the one head.  All four statements read
+    it from the context replica at the matching position, floor(dec_tp_rank * ctx_tp / dec_tp); the replicas
+    are given different contents here so that the choice shows."""
+    rng = np.random.default_rng(L)
+    B, D, nb_src, nb_dst = 2, 4, 6, 8
+    (ctx_tp, ctx_pp), (dec_tp, dec_pp) = ctx, dec
+    pools = {(p, t): (rng.integers(-2**15, 2**15, size=(nb_src, L // ctx_pp, 1, B, D), dtype=np.int16),
+                      rng.integers(-2**15, 2**15, size=(nb_src, L // ctx_pp, 1, B, D), dtype=np.int16))
+             for p in range(ctx_pp) for t in range(ctx_tp)}
+    src, dst = [4, 1, 1], [0, 7, 3]
+    for p in range(dec_pp):
+        for t in range(dec_tp):
+            replica = t * ctx_tp // dec_tp
+            assert O.contributing_workers(L, 1, ctx_tp, ctx_pp, dec_tp, t, dec_pp, p) == sorted(
+                {(gl // (L // ctx_pp), replica) for gl in range(p * L // dec_pp, (p + 1) * L // dec_pp)})
+            shape = (nb_dst, L // dec_pp, 1, B, D)
+            want_k = rng.integers(-2**15, 2**15, size=shape, dtype=np.int16)
+            init_k, init_v = want_k.copy(), want_k.copy()
+            want_v = want_k.copy()
+            for s_id, d_id in zip(src, dst):
+                for dl in range(L // dec_pp):
+                    gl = p * (L // dec_pp) + dl
+                    cp, cl = gl // (L // ctx_pp), gl % (L // ctx_pp)
+                    want_k[d_id, dl, 0] = pools[(cp, replica)][0][s_id, cl, 0]
+                    want_v[d_id, dl, 0] = pools[(cp, replica)][1][s_id, cl, 0]
+            for fn in (O.migrate_blocks_elementwise, O.migrate_blocks_numpy, OC.migrate_blocks_c):
+                k, v = init_k.copy(), init_v.copy()
+                fn(pools, ctx_tp, ctx_pp, src, dec_tp, t, dec_pp, p, dst, k, v, L, 1)
+                assert np.array_equal(k, want_k) and np.array_equal(v, want_v), fn.__name__
+            tk, tv = torch.from_numpy(init_k.copy()), torch.from_numpy(init_v.copy())
+            tpools = {key: (torch.from_numpy(a), torch.from_numpy(b)) for key, (a, b) in pools.items()}
+            O.migrate_blocks_torch(tpools, ctx_tp, ctx_pp, src, dec_tp, t, dec_pp, p, dst, tk, tv, L, 1)
+            assert np.array_equal(tk.numpy(), want_k) and np.array_equal(tv.numpy(), want_v)

@@ -77,3 +77,17 @@ def test_invalid_layouts_are_refused():
         ParallelConfig(2, 2, 1, 0)
     with pytest.raises(ValueError):
         KVModelConfig(40, 40, 128).get_num_heads(ParallelConfig(3, 0, 1, 0))
+
+
+def test_single_kv_head_geometry_mirrors_the_reference():
+    """distserve/config.py:233-237: a multi-query model has one KV head on every tensor-parallel rank."""
+    from distserve_b200.config import KVModelConfig, ParallelConfig, plan_overlaps
+
+    m = KVModelConfig(8, 1, 64)
+    for tp in (1, 2, 4):
+        for t in range(tp):
+            pc = ParallelConfig(tp, t, 2, 1)
+            assert m.get_num_heads(pc) == 1 and m.head_range(pc) == (0, 1) and m.get_num_layers(pc) == 4
+    ov = plan_overlaps(m, ParallelConfig(4, 0, 1, 0), ParallelConfig(2, 1, 2, 0))
+    assert [(o.ctx_pp_rank, o.ctx_tp_rank, o.src_layers, o.src_heads, o.dst_layers, o.dst_heads) for o in ov] == \
+        [(0, 2, (0, 4), (0, 1), (0, 4), (0, 1))]
