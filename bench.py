@@ -268,15 +268,14 @@ def reference_arm(args, w, trace, config, same_device):
 
     base = cpu_baseline(w, trace, same_device, passes=max(1, args.steps), warmup_passes=max(1, args.warmup))
     full_step_ms = base["ms_per_sample_pass"] * trace_blocks(trace) / max(1, base["sample_blocks"])
-    config = dict(config, sample_requests=base["sample_requests"], sample_blocks=base["sample_blocks"],
-                  sample_pool_blocks=base["sample_pool_blocks"],
-                  sample_note="each timed step is one pass over the sample, not over all requests of the workload")
+    assert (config["sample_requests"], config["sample_blocks"]) == (base["sample_requests"], base["sample_blocks"])
     return {"impl": "reference", "metric": METRIC, "value": base["value"], "unit": UNIT, "n_gpus": args.gpus,
             "steps": base["passes"], "warmup": base["warmup_passes"], "ms_per_step": full_step_ms,
             "ms_per_step_basis": "extrapolated: time of one sample pass x (blocks of a full step / blocks of the sample)",
             "ms_per_sample_pass": base["ms_per_sample_pass"], "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "u8", "data": "synthetic",
-            "config": config, "cpu_baseline": base,
+            "config": config, "step_is": "one pass over config.sample_requests requests, not over all requests of the workload",
+            "cpu_baseline": base,
             "e2e": {"value": base["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "note": "the reference's native copy (SwiftTransformer) is not in its tree; this arm is the CPU "
                     "restatement of its semantics (oracle/kv_oracle.py), torch host-tensor gather/scatter"}
@@ -801,6 +800,7 @@ def run_workload(args, w, world, rank, local_rank, dist, steps, warmup, primary=
 def describe(w, trace, same_device):
     from distserve_b200.workloads import trace_blocks
 
+    sample = cpu_sample(w, trace)
     return {
         "workload": f"{w.name}" + (" (context and decoding pools on one GPU)" if same_device else ""),
         "layers": w.model.num_layers, "kv_heads": w.model.num_kv_heads, "head_dim": w.model.head_dim,
@@ -810,6 +810,11 @@ def describe(w, trace, same_device):
         "bytes_per_block_per_dest_gpu": w.dec_block_bytes(),
         "l2": "each step moves far more than the 126 MB L2 (no reuse between steps' blocks)",
         "bytes_counted": "read+write (same GPU)" if same_device else "payload once (into the destination GPU)",
+        # the bounded sample the CPU arms run (cpu_baseline in this line; every timed step of --impl reference)
+        "sample_requests": len(sample), "sample_blocks": sum(len(d) for _, d in sample),
+        "sample_pool_blocks": CPU_SAMPLE_POOL_BLOCKS,
+        "sample_note": "CPU arms only: one pass = these requests, ids folded into compact host pools; the GPU arm runs "
+                       "all requests at full pool size",
     }
 
 
@@ -908,6 +913,8 @@ def main():
         "ms_per_step": r["ms_value"] / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "u8", "data": "synthetic", "config": describe(w, trace, same_device),
         "per_dest_gpu_GBps": value / max(1, n_dest), "dest_gpus": n_dest,
+        "scaling_note": "N = 1 is bound by HBM (bytes counted read + write), N >= 2 by the NVLink ingress of each destination "
+                        "GPU (payload counted once): compare per_dest_gpu_GBps across N >= 2, not value across N",
         "frac_of_nvlink_900_per_dest": None if same_device else value / max(1, n_dest) / NVLINK_NOMINAL_GBS,
         "p50_migrate_latency_ms": r["p50_ms"],
         "roofline": r["roofline"], "gpu_launches": r["launches"], "clocks": r["clocks"],
