@@ -413,11 +413,18 @@ def _run_replica(pool, devices, workload, steps, rate, weight_gb, pool_blocks, s
     cache = CacheConfig(w.block_size, 1 << 20)
     n_ctx, n_dec = w.ctx_tp * w.ctx_pp, w.dec_tp * w.dec_pp
     ctx_pc, dec_pc = w.ctx_config(), w.dec_config()
-    ctx_workers = [[pool.spawn(make_loop_worker, p * w.ctx_tp + t, "context", w.model, cache, [w.ctx_tp, t, w.ctx_pp, p],
-                               devices[(p * w.ctx_tp + t) % len(devices)]) for t in range(w.ctx_tp)] for p in range(w.ctx_pp)]
-    dec_workers = [[pool.spawn(make_loop_worker, n_ctx + p * w.dec_tp + t, "decoding", w.model, cache,
-                               [w.dec_tp, t, w.dec_pp, p], devices[(n_ctx + p * w.dec_tp + t) % len(devices)])
-                    for t in range(w.dec_tp)] for p in range(w.dec_pp)]
+    # the worker processes come up side by side (each spends most of its start-up importing torch)
+    from concurrent.futures import ThreadPoolExecutor
+
+    with ThreadPoolExecutor(max_workers=n_ctx + n_dec) as starter:
+        ctx_starting = [[starter.submit(pool.spawn, make_loop_worker, p * w.ctx_tp + t, "context", w.model, cache,
+                                        [w.ctx_tp, t, w.ctx_pp, p], devices[(p * w.ctx_tp + t) % len(devices)])
+                         for t in range(w.ctx_tp)] for p in range(w.ctx_pp)]
+        dec_starting = [[starter.submit(pool.spawn, make_loop_worker, n_ctx + p * w.dec_tp + t, "decoding", w.model, cache,
+                                        [w.dec_tp, t, w.dec_pp, p], devices[(n_ctx + p * w.dec_tp + t) % len(devices)])
+                         for t in range(w.dec_tp)] for p in range(w.dec_pp)]
+        ctx_workers = [[f.result() for f in row] for row in ctx_starting]
+        dec_workers = [[f.result() for f in row] for row in dec_starting]
     ctx_engine = ContextStageEngine(w.model, ctx_pc, cache, ctx_workers)
     dec_engine = DecodingStageEngine(w.model, dec_pc, cache, dec_workers,
                                      clear_migrated_blocks_callback=ctx_engine.clear_migrated_blocks)
