@@ -510,31 +510,32 @@ def run_workload(args, w, world, rank, local_rank, dist, steps, warmup, primary=
             for r in q.pop_finished_requests():
                 engine.block_manager.free_blocks(r.request_id)
 
+    sources = {}
+    steps_built = [0]
+
     def arrivals_of_one_step():
-        """What the context stage hands over in one step: a MigratingRequest per request of the trace."""
+        """What the context stage hands over in one step: a MigratingRequest per request of the trace.  The engine
+        runs on from step to step (requests of earlier steps are still decoding), so ids are unique across steps."""
+        base = steps_built[0] * 1_000_000
+        steps_built[0] += 1
         out = []
         for item in my_trace:
-            req = Request.of_length(item.request_id, item.prompt_len)
+            req = Request.of_length(base + item.request_id, item.prompt_len)
             req.append_token()                                  # the token the prefill step produced
             out.append(MigratingRequest(req, list(item.src_blocks), ctx_pc))
+            sources[base + item.request_id] = item.src_blocks
         return out
 
-    sources = {item.request_id: item.src_blocks for item in my_trace}
     # built ahead of the timed region: they are the step's input, produced by the context stage, not by this path
     prepared_arrivals = [arrivals_of_one_step() for _ in range(max(1, warmup) + steps)] if dec_worker is not None else []
 
     def step_engine():
         bm = engine.block_manager
-        sched.flush_pipeline()
-        for rid in list(bm.block_table):
-            bm.free_blocks(rid)
-        for q in sched.batch_queues:
-            q.requests = []
-        sched.waiting_queue, sched.swapped_queue = [], []
-        sched.unaccepted_queue = prepared_arrivals.pop() if prepared_arrivals else arrivals_of_one_step()
+        sched.unaccepted_queue.extend(prepared_arrivals.pop(0) if prepared_arrivals else arrivals_of_one_step())
         engine.lifetime_events.clear()
         floor = int(0.15 * w.dec_pool_blocks)
-        while sched.unaccepted_queue or sched._in_flight is not None:
+        # the step ends when its last group has been enqueued; that group is awaited by the next step's first call
+        while sched.unaccepted_queue:
             while bm.get_num_avail_gpu_blocks() < floor and sched.get_processing_num_requests():
                 retire_oldest(0.25)
             ready = sched.post_process_pipelined()
@@ -543,7 +544,11 @@ def run_workload(args, w, world, rank, local_rank, dist, steps, warmup, primary=
                 if sched.get_processing_num_requests() == 0:
                     raise SystemExit("bench: the decoding pool cannot hold the next request")
                 retire_oldest(0.5)
-        engine_records[:] = [(rid, tuple(sources[rid]), tuple(ids)) for rid, ids in bm.block_table.items()]
+
+    def engine_drain():
+        """Await the group still on the wire and note which blocks each resident request holds."""
+        sched.flush_pipeline()
+        engine_records[:] = [(rid, tuple(sources[rid]), tuple(ids)) for rid, ids in engine.block_manager.block_table.items()]
 
     def timed(step_fn, n_steps, **kw):
         """K steps between barriers; device time by CUDA events on the launching stream.  Returns the
@@ -650,6 +655,8 @@ def run_workload(args, w, world, rank, local_rank, dist, steps, warmup, primary=
         l0 = capi.get_counter("kernel_launches")
         ms_engine = timed(step_engine, steps)[0]
         engine_launches = capi.get_counter("kernel_launches") - l0
+        if dec_worker is not None:
+            engine_drain()
         launches += engine_launches
         if True:
             records = [spotcheck.TraceItem(rid, 0, src, dst) for rid, src, dst in engine_records]
