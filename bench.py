@@ -901,7 +901,7 @@ def main():
             try:
                 from distserve_b200 import e2e_loop
 
-                full = e2e_loop.run_actors(n_gpus=world, steps=300, time_scale=50.0)
+                full = e2e_loop.run_actors(n_gpus=world, steps=300, time_scale=50.0, deadline_s=300.0)
                 overlap = {k: full[k] for k in ("workload", "layout", "replicas", "hidden_fraction",
                                                 "added_us_per_migration_awaited", "added_us_per_migration_overlapped",
                                                 "verified", "steps", "time_scale", "overlapped_kernel_options")}

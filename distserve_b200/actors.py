@@ -144,9 +144,10 @@ class ActorPool:
         self.actors.append(handle)
         return handle
 
-    def stop(self) -> None:
+    def stop(self, timeout: float = 30.0) -> None:
+        """Ask every actor to leave, give each `timeout` seconds, then end the ones still there."""
         for a in self.actors:
-            a.stop()
+            a.stop(timeout)
         self.actors = []
 
     def __enter__(self) -> "ActorPool":

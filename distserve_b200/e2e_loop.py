@@ -543,11 +543,11 @@ def _run_replica(pool, devices, workload, steps, rate, weight_gb, pool_blocks, s
 
 def run_actors(n_gpus: int = 4, steps: int = 400, rate: float = 4.0, workload: str = "c5", weight_gb: float = 6.7,
                pool_blocks: int = 1024, seed: int = 7, time_scale: float = 50.0, overlapped_options: dict = None,
-               passes: int = 2, device_offset: int = 0) -> dict:
+               passes: int = 2, device_offset: int = 0, deadline_s: float = 600.0) -> dict:
     """The loop at the stated layout of the end-to-end configuration: every worker in its own process on its own
     GPU (context tp=2 on the first two GPUs, decoding tp=2 on the next two), driven from this process, which
     needs no GPU itself; with 8 GPUs a second, independent replica runs at the same time on GPUs 4-7.  With
-    fewer than 4 GPUs the workers share the GPUs that exist.  Arrivals are the reference generator's Poisson
+    fewer than 4 GPUs the workers share the GPUs that exist.  `deadline_s` bounds the whole run.  Arrivals are the reference generator's Poisson
     process at `rate` requests per second per replica, compressed by `time_scale` so that a short run sees
     many requests; prompt lengths follow the workload's distribution."""
     import threading
@@ -572,11 +572,19 @@ def run_actors(n_gpus: int = 4, steps: int = 400, rate: float = 4.0, workload: s
             except BaseException as e:      # surfaced below, after the other replica has ended
                 errors.append(e)
 
-        threads = [threading.Thread(target=one, args=(r,)) for r in range(n_replicas)]
+        threads = [threading.Thread(target=one, args=(r,), daemon=True) for r in range(n_replicas)]
+        started = time.perf_counter()
         for t in threads:
             t.start()
         for t in threads:
-            t.join()
+            t.join(max(0.0, deadline_s - (time.perf_counter() - started)))
+        if any(t.is_alive() for t in threads):
+            # A worker process that no longer answers must not hold the caller for ever: stopping the pool ends the
+            # worker processes this call started, which makes every pending call fail and the threads return.
+            pool.stop(timeout=2.0)
+            for t in threads:
+                t.join(30)
+            raise TimeoutError(f"the serving loop did not finish within {deadline_s:.0f} s")
     if errors:
         raise errors[0]
     fractions = [o["hidden_fraction"] for o in outs if o["hidden_fraction"] is not None]
