@@ -86,7 +86,7 @@ int64_t handle_checksum(const int64_t* w) {
 // 96 KiB.  Anything from 16 KiB in flight per SM upward saturates NVLink.
 struct Options {
     std::atomic<int64_t> kernel{0}, chunk_bytes{16384}, stages{3}, ctas_per_sm{0}, inline_tables{1}, overlap_launches{1}, max_ctas{0}, l2_hint{0},
-        dynamic_units{1}, wait_limit_ms{2000}, lose_unit_plus1{0}, unit_batch{0}, swap_wait{-1};
+        dynamic_units{1}, wait_limit_ms{2000}, lose_unit_plus1{0}, unit_batch{0}, swap_wait{-1}, wait_mode{0};
 };
 Options g_opt;
 std::atomic<uint64_t> g_option_gen{1};   // bumped by every kvmig_set_option
@@ -912,7 +912,14 @@ int wait_ticket(uint64_t ticket) {
         cudaEvent_t done = sl.done;
         lock.unlock();
         const int64_t t0 = now_ns();
-        cudaError_t e = cudaEventSynchronize(done);
+        cudaError_t e;
+        if (g_opt.wait_mode.load() == 1) {
+            // Busy-poll the event from this thread instead of leaving the kind of wait to the device's scheduling flag.
+            while ((e = cudaEventQuery(done)) == cudaErrorNotReady) {}
+            if (e != cudaSuccess) (void)cudaGetLastError();
+        } else {
+            e = cudaEventSynchronize(done);
+        }
         g_cnt.ns_wait += now_ns() - t0;
         lock.lock();
         if (e != cudaSuccess) rc = fail(KVMIG_ECUDA, "waiting for the migration kernel: %s", cudaGetErrorString(e));
@@ -1265,6 +1272,7 @@ static std::atomic<int64_t>* option_slot(const char* name) {
     if (!std::strcmp(name, "unit_batch")) return &g_opt.unit_batch;
     if (!std::strcmp(name, "lose_unit_plus1")) return &g_opt.lose_unit_plus1;
     if (!std::strcmp(name, "swap_wait")) return &g_opt.swap_wait;
+    if (!std::strcmp(name, "wait_mode")) return &g_opt.wait_mode;
     return nullptr;
 }
 

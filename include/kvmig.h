@@ -282,6 +282,9 @@ KVMIG_API int kvmig_swap(const int64_t* source_block_ids, int64_t num_source,
  *             "lose_unit_plus1" N > 0 = failure-path exercise: work unit N-1
  *             arms its completion barrier but never issues its load, so that
  *             wait runs out (default 0),
+ *             "wait_mode" 1 = kvmig_migrate_wait / kvmig_migrate_blocks poll the
+ *             kernel's event from the calling thread instead of calling
+ *             cudaEventSynchronize (default 0),
  *             "swap_wait" 1 = kvmig_swap returns only after its copies have
  *             finished (default 0, or the value of KVMIG_SWAP_WAIT in the
  *             environment when the option was never set)
