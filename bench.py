@@ -529,7 +529,19 @@ def run_workload(args, w, world, rank, local_rank, dist, steps, warmup, primary=
     # built ahead of the timed region: they are the step's input, produced by the context stage, not by this path
     prepared_arrivals = [arrivals_of_one_step() for _ in range(max(1, warmup) + steps)] if dec_worker is not None else []
 
+    engine_error = []
+
     def step_engine():
+        """One step through scheduler and engine.  A failure of this leg is reported in its own entry of the line; it
+        must not keep this rank from the collectives the other ranks are waiting in."""
+        if engine_error:
+            return
+        try:
+            run_engine_step()
+        except Exception as e:
+            engine_error.append(f"{type(e).__name__}: {e}"[:300])
+
+    def run_engine_step():
         bm = engine.block_manager
         sched.unaccepted_queue.extend(prepared_arrivals.pop(0) if prepared_arrivals else arrivals_of_one_step())
         engine.lifetime_events.clear()
@@ -542,7 +554,7 @@ def run_workload(args, w, world, rank, local_rank, dist, steps, warmup, primary=
             sched.get_next_batch()
             if not ready and sched._in_flight is None and sched.unaccepted_queue:
                 if sched.get_processing_num_requests() == 0:
-                    raise SystemExit("bench: the decoding pool cannot hold the next request")
+                    raise RuntimeError("the decoding pool cannot hold the next request")
                 retire_oldest(0.5)
 
     def engine_drain():
@@ -655,10 +667,20 @@ def run_workload(args, w, world, rank, local_rank, dist, steps, warmup, primary=
         l0 = capi.get_counter("kernel_launches")
         ms_engine = timed(step_engine, steps)[0]
         engine_launches = capi.get_counter("kernel_launches") - l0
-        if dec_worker is not None:
-            engine_drain()
+        if dec_worker is not None and not engine_error:
+            try:
+                engine_drain()
+            except Exception as e:
+                engine_error.append(f"{type(e).__name__}: {e}"[:300])
+        failed = torch.tensor([1.0 if engine_error else 0.0], dtype=torch.float64)
+        if dist is not None:
+            dist.all_reduce(failed)
+        if failed.item() > 0:
+            ms_engine = None
+            if not engine_error:
+                engine_error.append("this leg failed on another rank")
         launches += engine_launches
-        if True:
+        if ms_engine is not None:
             records = [spotcheck.TraceItem(rid, 0, src, dst) for rid, src, dst in engine_records]
             if dist is not None:
                 gathered = [None] * world
@@ -794,6 +816,7 @@ def run_workload(args, w, world, rank, local_rank, dist, steps, warmup, primary=
         "p50_ms": p50[0].item() * 1e3 if lat or dist is not None else None,
         "roofline": roof, "launches": int(totals[1].item()), "clocks": clocks, "verified": verified,
         "verification": verification, "engine_verification": engine_verification, "swap": swap_info, "host_us": host_us,
+        "engine_error": engine_error[0] if engine_error else None,
         "peer_copy": peer_copy,
     }
     # release the pools before another workload is set up in this process
@@ -956,6 +979,8 @@ def main():
                                "api": "DecodingStageFCFSScheduler.post_process_pipelined -> DecodingStageEngine."
                                       "begin/finish_migrate_blocks_batched -> KVWorker.migrate_blocks_async, Python lists, "
                                       "target blocks from the block manager"}
+    elif r["engine_error"]:
+        line["e2e_batched"] = {"error": r["engine_error"]}
     if r["swap"] is not None:
         line["swap"] = r["swap"]
     if r["peer_copy"] is not None:
