@@ -884,6 +884,8 @@ def main():
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the migration path has no CPU implementation")
     distserve_b200.load_ops()
+    # one GPU per rank; on a machine with fewer GPUs than ranks (functional runs only) the ranks share them
+    local_rank = local_rank % torch.cuda.device_count()
     torch.cuda.set_device(local_rank)
     for opt in ("kernel", "chunk_bytes", "stages", "ctas_per_sm"):
         v = getattr(args, opt)

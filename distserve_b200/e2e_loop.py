@@ -387,7 +387,8 @@ class LoopWorker(KVWorker):
 
 
 def make_loop_worker(worker_id: int, stage: str, model: KVModelConfig, cache: CacheConfig, pc_list, device: int) -> LoopWorker:
-    """Factory run inside the worker process."""
+    """Factory run inside the worker process.  On a machine with fewer GPUs than workers the workers share them."""
+    device = device % torch.cuda.device_count()
     torch.cuda.set_device(device)
     tp, t, pp, p = pc_list
     return LoopWorker(worker_id, stage, model, cache, ParallelConfig(tp, t, pp, p), device=device)
