@@ -89,6 +89,7 @@ def parse_args(argv=None):
     ap.add_argument("--no-other-workloads", action="store_true", help="N=1: skip the short c1 and c5 runs")
     ap.add_argument("--no-overlap", action="store_true", help="N=4/8: skip the serving loop with stand-in decode steps")
     ap.add_argument("--only-value", action="store_true", help="time the value region only (profiler captures)")
+    ap.add_argument("--wave-blocks", type=int, default=4096, help="most blocks one launch of the `batched` leg carries")
     ap.add_argument("--peer-in-process", action="store_true",
                     help="one process, two GPUs: every context worker on GPU 0, decoding worker (0,0) on GPU 1 "
                          "(a single-process cross-GPU case, e.g. for a profiler capture)")
@@ -458,7 +459,7 @@ def run_workload(args, w, world, rank, local_rank, dist, steps, warmup, primary=
     # several requests per launch: waves of consecutive requests whose target blocks are all distinct
     waves, cur_src, cur_dst, seen_dst = [], [], [], set()
     for item in my_trace:
-        if seen_dst.intersection(item.dst_blocks) or len(cur_src) + len(item.src_blocks) > 4096:
+        if cur_src and (seen_dst.intersection(item.dst_blocks) or len(cur_src) + len(item.src_blocks) > args.wave_blocks):
             waves.append((capi.I64List(cur_src), capi.I64List(cur_dst)))
             cur_src, cur_dst, seen_dst = [], [], set()
         cur_src += item.src_blocks
@@ -971,7 +972,7 @@ def main():
         line["batched"] = {"value": r["batched_value"], "unit": UNIT, "per_dest_gpu_GBps": per_dest(r["batched_value"]),
                            "launches_per_step_per_dest": r["waves"],
                            "api": "kvmig_migrate_blocks_async with the concatenated block lists of consecutive requests "
-                                  "(up to 4096 blocks, distinct targets) per launch"}
+                                  f"(up to {args.wave_blocks} blocks, distinct targets) per launch"}
     if r["engine_value"] is not None:
         line["e2e_batched"] = {"value": r["engine_value"], "unit": UNIT, "ms_per_step": r["ms_engine"] / args.steps,
                                "per_dest_gpu_GBps": per_dest(r["engine_value"]),
