@@ -666,7 +666,10 @@ def run_workload(args, w, world, rank, local_rank, dist, steps, warmup, primary=
             if dec_worker is not None:
                 step_engine()
         l0 = capi.get_counter("kernel_launches")
+        w0, t0 = capi.get_counter("ns_wait"), time.perf_counter()
         ms_engine = timed(step_engine, steps)[0]
+        engine_wall_ms = (time.perf_counter() - t0) * 1e3 / steps
+        engine_waited_ms = (capi.get_counter("ns_wait") - w0) / 1e6 / steps
         engine_launches = capi.get_counter("kernel_launches") - l0
         if dec_worker is not None and not engine_error:
             try:
@@ -818,6 +821,7 @@ def run_workload(args, w, world, rank, local_rank, dist, steps, warmup, primary=
         "roofline": roof, "launches": int(totals[1].item()), "clocks": clocks, "verified": verified,
         "verification": verification, "engine_verification": engine_verification, "swap": swap_info, "host_us": host_us,
         "engine_error": engine_error[0] if engine_error else None,
+        "engine_host_ms": None if ms_engine is None else {"wall_per_step": engine_wall_ms, "waiting_for_the_gpu_per_step": engine_waited_ms},
         "peer_copy": peer_copy,
     }
     # release the pools before another workload is set up in this process
@@ -979,6 +983,7 @@ def main():
                                "frac_of_nvlink_900_per_dest": None if same_device else per_dest(r["engine_value"]) / NVLINK_NOMINAL_GBS,
                                "launches_per_step_per_dest": r["engine_launches_per_step"],
                                "verification": r["engine_verification"],
+                               "host_ms_rank0": r["engine_host_ms"],
                                "api": "DecodingStageFCFSScheduler.post_process_pipelined -> DecodingStageEngine."
                                       "begin/finish_migrate_blocks_batched -> KVWorker.migrate_blocks_async, Python lists, "
                                       "target blocks from the block manager"}

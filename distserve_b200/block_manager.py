@@ -44,7 +44,8 @@ class _IdPool:
             call_all_workers(self.flush_method)
             self.free.extend(self.parked)
             self.parked = []
-        taken, self.free = self.free[:count], self.free[count:]
+        taken = self.free[:count]
+        del self.free[:count]      # in place: the list can be as long as the pool
         return taken
 
     def used(self) -> int:

@@ -65,12 +65,18 @@ class DecodingStageFCFSScheduler:
         """Blocks the accepted-but-not-running requests hold (their prompts)."""
         return sum(self._blocks(r.get_input_len()) for r in self.waiting_queue)
 
-    def _fits_current_batch(self, request: Request) -> bool:
+    def _fits_current_batch(self, request: Request, running: Optional[int] = None, waiting: Optional[int] = None,
+                            batch_tokens: Optional[int] = None) -> bool:
+        """The reference's admission rule (distserve/decoding_stage_scheduler.py:155-181).  The three totals may be
+        handed in by a caller that keeps them up to date while it moves requests; otherwise they are recomputed."""
         batch = self.batch_queues[self.cur_index]
+        running = self._running_blocks() if running is None else running
+        waiting = self._waiting_blocks() if waiting is None else waiting
+        batch_tokens = batch.get_num_input_tokens() if batch_tokens is None else batch_tokens
         return (len(batch) < self.sched_config.max_batch_size
-                and batch.get_num_input_tokens() + request.get_num_input_tokens() <= self.sched_config.max_tokens_per_batch
-                and self._running_blocks() + self._waiting_blocks()
-                + self._blocks(request.get_input_len() + request.get_output_len()) <= self.block_manager.max_num_gpu_blocks)
+                and batch_tokens + request.get_num_input_tokens() <= self.sched_config.max_tokens_per_batch
+                and running + waiting + self._blocks(request.get_input_len() + request.get_output_len())
+                <= self.block_manager.max_num_gpu_blocks)
 
     # --- requests -----------------------------------------------------------------------
     def add_request(self, migrating_req: MigratingRequest) -> None:
@@ -92,26 +98,32 @@ class DecodingStageFCFSScheduler:
     def get_next_batch(self) -> BatchedRequests:
         self.cur_index = (self.cur_index + 1) % self.parallel_config.pipeline_parallel_size
         batch = self.batch_queues[self.cur_index]
+        # The block and token totals the rules below look at are summed once and then kept up to date as requests
+        # move between the queues (the sums run over every running request; recomputing them per candidate is what
+        # makes an iteration's host time grow with the batch).
+        running, waiting, tokens = self._running_blocks(), self._waiting_blocks(), batch.get_num_input_tokens()
         # Not enough GPU blocks for what is running and waiting: swap out the newest member of this batch.
-        while self._running_blocks() + self._waiting_blocks() > self.block_manager.max_num_gpu_blocks:
+        while running + waiting > self.block_manager.max_num_gpu_blocks:
             victim = batch.requests.pop(-1)
+            running -= self._blocks(victim.get_input_len() + victim.get_output_len())
+            tokens -= victim.get_num_input_tokens()
             self.swapped_queue.append(victim)
             self.block_manager.swap_out_requests([victim])
         # Refill: swapped-out requests first, then waiting ones, each only while it fits.
         while self.swapped_queue or self.waiting_queue:
-            if self.swapped_queue:
-                request = self.swapped_queue[0]
-                if not self._fits_current_batch(request):
-                    break
+            from_swapped = bool(self.swapped_queue)
+            request = self.swapped_queue[0] if from_swapped else self.waiting_queue[0]
+            if not self._fits_current_batch(request, running, waiting, tokens):
+                break
+            if from_swapped:
                 self.block_manager.swap_in_requests([request])
-                batch.add_request(request)
                 self.swapped_queue.pop(0)
             else:
-                request = self.waiting_queue[0]
-                if not self._fits_current_batch(request):
-                    break
-                batch.add_request(request)
                 self.waiting_queue.pop(0)
+                waiting -= self._blocks(request.get_input_len())
+            batch.add_request(request)
+            running += self._blocks(request.get_input_len() + request.get_output_len())
+            tokens += request.get_num_input_tokens()
         return batch
 
     def _should_accept(self, prompt_len: int, waiting_blocks: int, avail_blocks: int) -> bool:
