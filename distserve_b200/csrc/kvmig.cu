@@ -756,6 +756,7 @@ int enqueue_migration(int64_t ctx_pp, int64_t ctx_tp, const int64_t* ctx_blocks,
     bool cross_stream_wait = false;
     int running[KVMIG_MAX_INFLIGHT];
     for (int& r : running) r = -1;
+    bool event_awaited[KVMIG_MAX_INFLIGHT] = {};   // slots whose event this stream has already been told to wait for
     const Range my_writes[2] = {Range{static_cast<const char*>(k_cache), (size_t)(shape->num_blocks * block_bytes(*shape))},
                                 Range{static_cast<const char*>(v_cache), (size_t)(shape->num_blocks * block_bytes(*shape))}};
     auto must_follow = [&](int si) -> int {
@@ -763,8 +764,9 @@ int enqueue_migration(int64_t ctx_pp, int64_t ctx_tp, const int64_t* ctx_blocks,
         Slot& other = st.slots[si];
         if (!slot_running(st, si, running)) return 0;
         depends = true;
-        if (other.stream != stream) {
+        if (other.stream != stream && !event_awaited[si]) {
             CU_TRY(cudaStreamWaitEvent(stream, other.done, 0));
+            event_awaited[si] = true;
             cross_stream_wait = true;
         }
         return 0;
