@@ -26,7 +26,7 @@
 extern "C" {
 #endif
 
-#define KVMIG_ABI_VERSION 1
+#define KVMIG_ABI_VERSION 2   /* 2: handles carry a per-process number; kvmig_handle_is_local */
 
 #if defined(__GNUC__)
 #define KVMIG_API __attribute__((visibility("default")))

@@ -28,7 +28,7 @@ def test_header_and_binding_agree(built_libs):
     lib = ctypes.CDLL(str(built_libs[0]))
     for name in names:
         assert hasattr(lib, name), f"{name} is declared in include/kvmig.h but not exported"
-    assert capi.lib().kvmig_abi_version() == 1
+    assert capi.lib().kvmig_abi_version() == 2
     m = re.search(r"#define KVMIG_HANDLE_WORDS (\d+)", HEADER.read_text())
     assert int(m.group(1)) == capi.HANDLE_WORDS
 
