@@ -410,9 +410,18 @@ def poisson_arrival_steps(rate_per_s: float, step_ms: float, steps: int, seed: i
         out.append(int(t * 1e3 / step_ms))
 
 
-def _run_replica(pool, devices, workload, steps, rate, weight_gb, pool_blocks, seed, time_scale, options, passes, tag) -> dict:
+def _one_shard_of(w):
+    """The workload as ONE tensor-parallel rank of each stage sees it (equal layouts only): that rank's share of the
+    KV heads, tp = 1 on both sides.  Two worker processes instead of 2 x tp."""
+    from dataclasses import replace
+
+    assert w.ctx_tp == w.dec_tp and w.ctx_pp == w.dec_pp == 1, "a single shard stands for the stage only with equal layouts"
+    model = KVModelConfig(w.model.num_layers, w.model.num_kv_heads // w.dec_tp, w.model.head_dim, w.model.dtype)
+    return replace(w, name=w.name + "-one-shard", model=model, ctx_tp=1, dec_tp=1)
+
+
+def _run_replica(pool, devices, w, steps, rate, weight_gb, pool_blocks, seed, time_scale, options, passes, tag) -> dict:
     """Context tp x pp workers on the first devices, decoding tp x pp workers on the next ones; one replica."""
-    w = WORKLOADS[workload]
     cache = CacheConfig(w.block_size, 1 << 20)
     n_ctx, n_dec = w.ctx_tp * w.ctx_pp, w.dec_tp * w.dec_pp
     ctx_pc, dec_pc = w.ctx_config(), w.dec_config()
@@ -546,18 +555,20 @@ def _run_replica(pool, devices, workload, steps, rate, weight_gb, pool_blocks, s
 
 def run_actors(n_gpus: int = 4, steps: int = 400, rate: float = 4.0, workload: str = "c5", weight_gb: float = 6.7,
                pool_blocks: int = 1024, seed: int = 7, time_scale: float = 50.0, overlapped_options: dict = None,
-               passes: int = 2, device_offset: int = 0, deadline_s: float = 600.0) -> dict:
+               passes: int = 2, device_offset: int = 0, deadline_s: float = 600.0, one_shard: bool = False) -> dict:
     """The loop at the stated layout of the end-to-end configuration: every worker in its own process on its own
     GPU (context tp=2 on the first two GPUs, decoding tp=2 on the next two), driven from this process, which
     needs no GPU itself; with 8 GPUs a second, independent replica runs at the same time on GPUs 4-7.  With
-    fewer than 4 GPUs the workers share the GPUs that exist.  `deadline_s` bounds the whole run.  Arrivals are the reference generator's Poisson
+    fewer than 4 GPUs the workers share the GPUs that exist; `one_shard` runs one tensor-parallel rank of each stage
+    instead (two worker processes: what a 2-GPU machine can run without two workers sharing a GPU).  `deadline_s`
+    bounds the whole run.  Arrivals are the reference generator's Poisson
     process at `rate` requests per second per replica, compressed by `time_scale` so that a short run sees
     many requests; prompt lengths follow the workload's distribution."""
     import threading
 
     from .actors import ActorPool
 
-    w = WORKLOADS[workload]
+    w = _one_shard_of(WORKLOADS[workload]) if one_shard else WORKLOADS[workload]
     per_replica = w.ctx_tp * w.ctx_pp + w.dec_tp * w.dec_pp
     n_replicas = max(1, n_gpus // per_replica)
     options = dict(SIDE_BY_SIDE_OPTIONS if overlapped_options is None else overlapped_options)
@@ -570,7 +581,7 @@ def run_actors(n_gpus: int = 4, steps: int = 400, rate: float = 4.0, workload: s
                     devices = [device_offset + r * per_replica + i for i in range(per_replica)]
                 else:
                     devices = [device_offset + i for i in range(max(1, n_gpus))]
-                outs[r] = _run_replica(pool, devices, workload, steps, rate, weight_gb, pool_blocks, seed + r, time_scale,
+                outs[r] = _run_replica(pool, devices, w, steps, rate, weight_gb, pool_blocks, seed + r, time_scale,
                                        options, passes, r)
             except BaseException as e:      # surfaced below, after the other replica has ended
                 errors.append(e)
@@ -607,6 +618,7 @@ def main() -> None:
     ap.add_argument("--swap", action="store_true", help="measure swap-out/in beside decode steps instead of migration")
     ap.add_argument("--actors", action="store_true", help="one worker process per GPU, context tp2 -> decoding tp2 per 4 GPUs")
     ap.add_argument("--pool-blocks", type=int, default=1024)
+    ap.add_argument("--one-shard", action="store_true", help="with --actors: one tensor-parallel rank of each stage (2 processes)")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=400)
     ap.add_argument("--rate", type=float, default=4.0)
@@ -622,7 +634,7 @@ def main() -> None:
     options = None if args.opt is None else {k: int(v) for k, v in (pair.split("=") for pair in args.opt)}
     if args.actors:
         print(json.dumps(run_actors(args.gpus, args.steps, args.rate, args.workload, args.weight_gb, pool_blocks=args.pool_blocks,
-                                    time_scale=args.time_scale, overlapped_options=options)))
+                                    time_scale=args.time_scale, overlapped_options=options, one_shard=args.one_shard)))
         return
     print(json.dumps(run(args.gpus, args.steps, args.rate, args.workload, args.weight_gb, time_scale=args.time_scale,
                          overlapped_options=options)))
