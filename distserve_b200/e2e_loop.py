@@ -361,22 +361,20 @@ class LoopWorker(KVWorker):
         """One iteration of the decoding loop on this worker.  `migrations` = [(source ids, target ids)] of the
         requests accepted at this step boundary; `wait_tickets` = tickets of copies enqueued at an earlier
         boundary whose requests join the batch now.  serial: each accepted request is pulled with the awaited
-        operator before the step; overlapped: the step is launched and the pulls are then enqueued on the side
-        stream.  Returns (tickets of the copies enqueued now, seconds spent in awaited pulls)."""
+        operator before the step; overlapped: the pulls are enqueued on the side stream and the step starts at
+        once.  Returns (tickets of the copies enqueued now, seconds spent in awaited pulls)."""
         with torch.cuda.device(self.device):
             for t in wait_tickets:
                 self.migrate_wait(t)
             tickets, awaited = [], 0.0
-            if mode == "serial":
-                for src, dst in migrations:
+            for src, dst in migrations:
+                if mode == "serial":
                     t0 = time.perf_counter()
                     self.migrate_blocks(src, context_parallel_config, dst)
                     awaited += time.perf_counter() - t0
-            self.decoder.step()
-            if mode == "overlapped":
-                # enqueued once the step is on its way: the host's share of the enqueue runs beside the step as well
-                for src, dst in migrations:
+                elif mode == "overlapped":
                     tickets.append(self.migrate_blocks_async(src, context_parallel_config, dst, stream=self.side))
+            self.decoder.step()
             torch.cuda.current_stream().synchronize()      # a real step returns sampled tokens to the host
             return tickets, awaited
 
