@@ -6,6 +6,7 @@ foreign-language host would; the torch operator shim is the other client.
 from __future__ import annotations
 
 import ctypes as C
+from array import array
 from typing import Optional, Sequence
 
 from . import kvmig_library_path
@@ -85,7 +86,8 @@ def _check(rc: int) -> None:
 def as_i64(values: Sequence[int]):
     """A ctypes int64 array holding `values`; block lists that are passed again and again can be converted
     once and handed to the calls below in this form."""
-    return (C.c_int64 * max(1, len(values)))(*values)
+    packed = array("q", values) if len(values) else array("q", (0,))      # one pass in C; non-integers raise TypeError
+    return (C.c_int64 * len(packed)).from_buffer(packed)                 # shares (and keeps alive) the packed buffer
 
 
 class I64List:
