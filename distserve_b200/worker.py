@@ -131,7 +131,12 @@ class KVWorker:
            context_block_indexes, pp, tp, pp_rank, tp_rank, decoding_block_indexes, self.k_cache, self.v_cache)
 
     def _pool_shape(self) -> capi.PoolShape:
-        return capi.PoolShape.of(*self.k_cache.shape, self.k_cache.element_size())
+        """The pools' shape as the C ABI takes it; built once per pool (the pools live as long as the worker)."""
+        cached = getattr(self, "_shape_of_pool", None)
+        if cached is None or cached[0] is not self.k_cache:
+            cached = (self.k_cache, capi.PoolShape.of(*self.k_cache.shape, self.k_cache.element_size()))
+            self._shape_of_pool = cached
+        return cached[1]
 
     def migrate_blocks_async(self, context_block_indexes: List[int], context_parallel_config: ParallelConfig,
                              decoding_block_indexes: List[int], stream: Optional[torch.cuda.Stream] = None) -> int:
