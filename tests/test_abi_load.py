@@ -198,3 +198,20 @@ print('LOADED', distserve.LIB_PATH)
     proc = subprocess.run([sys.executable, "-W", "ignore", "-c", code], capture_output=True, text=True, env=env, timeout=300)
     assert proc.returncode == 0, proc.stderr[-2000:]
     assert f"LOADED {built_libs[1]}" in proc.stdout
+
+
+def test_block_lists_are_packed_as_int64(built_libs):
+    """The binding hands block lists to the C ABI as int64 arrays: values survive, an empty list still yields a
+    valid pointer, numpy integers are accepted and non-integers refused."""
+    import numpy as np
+
+    from distserve_b200 import capi
+
+    arr = capi.as_i64([5, 0, 2**40, -1])
+    assert list(arr) == [5, 0, 2**40, -1] and len(arr) == 4
+    assert len(capi.as_i64([])) == 1                      # never a zero-length ctypes array
+    assert list(capi.as_i64((np.int64(7), np.int32(3)))) == [7, 3]
+    with pytest.raises(TypeError):
+        capi.as_i64([1.5])
+    boxed = capi.I64List(range(10))
+    assert len(boxed) == 10 and list(boxed.array) == list(range(10))
