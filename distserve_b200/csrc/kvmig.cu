@@ -83,9 +83,10 @@ int64_t handle_checksum(const int64_t* w) {
 // 296 CTAs), CTAs drawing two consecutive units (32 KiB) per visit to the work counter.  With consecutive
 // launches overlapping, same-GPU copies of OPT-13B-shaped blocks run at 6.8-6.9 TB/s for any setting from 64 to
 // 192 KiB in flight per SM; awaited single calls, which pay their own ramp-up and tail, were fastest around
-// 96 KiB.  Anything from 16 KiB in flight per SM upward saturates NVLink.
+// 96 KiB.  Anything from 16 KiB in flight per SM upward saturates NVLink.  Calls that carry several requests
+// (more than 256 blocks) run long enough to gain about 1 % from a fourth stage, so "stages" 0 means 3 or 4.
 struct Options {
-    std::atomic<int64_t> kernel{0}, chunk_bytes{16384}, stages{3}, ctas_per_sm{0}, inline_tables{1}, overlap_launches{1}, max_ctas{0}, l2_hint{0},
+    std::atomic<int64_t> kernel{0}, chunk_bytes{16384}, stages{0}, ctas_per_sm{0}, inline_tables{1}, overlap_launches{1}, max_ctas{0}, l2_hint{0},
         dynamic_units{1}, wait_limit_ms{2000}, lose_unit_plus1{0}, unit_batch{0}, swap_wait{-1}, wait_mode{0};
 };
 Options g_opt;
@@ -175,6 +176,18 @@ struct LaunchShape {
     int vec = 16;              // widest vector every address and length allows
     int64_t stages = 0, chunk = 0, ctas_per_sm = 0;
     size_t smem = 0;
+    int64_t stages_long = 0;   // ring depth and shared memory for calls of more than kInlineSmall blocks
+    size_t smem_long = 0;
+
+    // The shape to launch a call of n blocks with.
+    LaunchShape for_blocks(int64_t n, int64_t long_from) const {
+        LaunchShape out = *this;
+        if (n > long_from && stages_long > 0) {
+            out.stages = stages_long;
+            out.smem = smem_long;
+        }
+        return out;
+    }
 };
 
 // Everything about a call that does not depend on its block lists.  A worker migrates request after request
@@ -548,22 +561,31 @@ int shape_launch(DeviceState& st, uintptr_t align_bits, LaunchShape* ls) {
     if (ls->kernel == 0) ls->kernel = (ls->vec == 16) ? 2 : 1;
     if (ls->kernel == 2 && ls->vec != 16)
         return fail(KVMIG_EINVAL, "the bulk-copy kernel needs 16-byte aligned runs; this shape gives %d", ls->vec);
-    ls->stages = std::min<int64_t>(std::max<int64_t>(g_opt.stages.load(), 2), kMaxStages);
+    // "stages" 0 = automatic: 3, and one more for calls of more than kInlineSmall blocks (several requests in one
+    // launch), which run long enough to gain from a third more bytes in flight; a positive value is used for every call.
+    const int64_t asked = g_opt.stages.load();
+    ls->stages = asked > 0 ? std::min<int64_t>(std::max<int64_t>(asked, 2), kMaxStages) : 3;
+    ls->stages_long = asked > 0 ? ls->stages : 4;
     ls->chunk = g_opt.chunk_bytes.load();
     if (ls->chunk < 16 || ls->chunk % 16) return fail(KVMIG_EINVAL, "chunk_bytes must be a positive multiple of 16");
     ls->ctas_per_sm = g_opt.ctas_per_sm.load();
     if (ls->kernel == 2) {
         ls->smem = (size_t)ls->stages * ls->chunk + (size_t)ls->stages * (8 + 8 + 4 + 4) + 16;
+        ls->smem_long = (size_t)ls->stages_long * ls->chunk + (size_t)ls->stages_long * (8 + 8 + 4 + 4) + 16;
         if ((int64_t)ls->smem > st.max_smem_optin)
             return fail(KVMIG_ELIMIT, "stages x chunk_bytes = %zu B exceeds the %d B of shared memory a CTA may use", ls->smem,
                         st.max_smem_optin);
+        if ((int64_t)ls->smem_long > st.max_smem_optin) {   // the extra stage does not fit: long calls keep the base ring
+            ls->stages_long = ls->stages;
+            ls->smem_long = ls->smem;
+        }
         if (ls->ctas_per_sm <= 0) {
             const int64_t ring = ls->stages * ls->chunk, target = 96 * 1024;   // bytes in flight per SM
             ls->ctas_per_sm = std::max<int64_t>(1, std::min<int64_t>(8, (target + ring - 1) / ring));
             ls->ctas_per_sm = std::min<int64_t>(ls->ctas_per_sm, std::max<int64_t>(1, (220 * 1024) / (int64_t)(ls->smem + 1024)));
         }
-        if ((int)ls->smem > st.bulk_smem_set) {
-            const int bytes = (int)ls->smem;
+        if ((int)std::max(ls->smem, ls->smem_long) > st.bulk_smem_set) {
+            const int bytes = (int)std::max(ls->smem, ls->smem_long);
             CU_TRY(cudaFuncSetAttribute(kv_migrate_bulk, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
             CU_TRY(cudaFuncSetAttribute(kv_migrate_bulk_inline<kInlineSmall>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
             CU_TRY(cudaFuncSetAttribute(kv_migrate_bulk_inline<kInlineLarge>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
@@ -721,7 +743,7 @@ int enqueue_migration(int64_t ctx_pp, int64_t ctx_tp, const int64_t* ctx_blocks,
         pr.valid = true;
     }
     const Assembly& as = pr.as;
-    const LaunchShape& ls = pr.ls;
+    const LaunchShape ls = pr.ls.for_blocks(n_ctx, kInlineSmall);
     const int64_t t_prepared = now_ns();
     g_cnt.ns_prepare += t_prepared - t_begin;
 
@@ -1007,9 +1029,10 @@ int migrate_static(int64_t ctx_pp, int64_t ctx_tp, const int64_t* ctx_blocks, in
     rc = validate_ids(st, ctx_blocks, dec_blocks, n_ctx, as.src_num_blocks, shape->num_blocks);
     if (rc) return rc;
     if (n_ctx == 0) return 0;
-    LaunchShape ls;
-    rc = shape_launch(st, as.align_bits, &ls);
+    LaunchShape base;
+    rc = shape_launch(st, as.align_bits, &base);
     if (rc) return rc;
+    const LaunchShape ls = base.for_blocks(n_ctx, kInlineSmall);
 
     MigParams p;
     int64_t bytes_per_block = 0;

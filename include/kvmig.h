@@ -260,7 +260,9 @@ KVMIG_API int kvmig_swap(const int64_t* source_block_ids, int64_t num_source,
  * Tuning and introspection (no counterpart in the reference).
  *   options : "kernel" 0 auto | 1 vector loads | 2 bulk-copy pipeline,
  *             "chunk_bytes" size of one work unit = one shared-memory stage
- *             (default 16384), "stages" ring depth per CTA (default 3),
+ *             (default 16384), "stages" ring depth per CTA (default 0 =
+ *             automatic: 3, and 4 for calls of more than 256 blocks; a
+ *             positive value applies to every call),
  *             "ctas_per_sm" (default 0 = as many as keep 96 KiB in flight per
  *             SM: 2 with the defaults),
  *             "inline_tables" 1 = lists of up to 1024 blocks travel in the
